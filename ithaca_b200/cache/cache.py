@@ -4,7 +4,7 @@ Each mixer states what it keeps per sequence: keys and values that grow with the
 sequence (``KVRequest``) and/or a state of fixed size (``StateRequest``).  Cache
 entries with equal key/value needs share a group: one pool of pages, one block
 table per slot, and one pair of tensors ``[entries, pages, kv_heads, page_size,
-head_dim]``.  Fixed-size state lies beside it as ``[entries, max_slots, *shape]``
+head_dim]`` (the values' last size is their own head size where a mixer gives one).  Fixed-size state lies beside it as ``[entries, max_slots, *shape]``
 and is cleared when a slot is handed out (the reference zeroes recurrent state
 when a sequence restarts, src/model.cpp:1047-1055).
 
@@ -30,6 +30,7 @@ class KVRequest:
     n_kv_heads: int
     head_dim: int
     window: Optional[int] = None
+    v_head_dim: Optional[int] = None        # size of a value head when it differs from the key head's
 
 
 @dataclass(frozen=True)
@@ -70,14 +71,14 @@ def plan_groups(requests: Mapping[int, Sequence[object]]):
                 if seen_kv:
                     raise CacheError(f"cache entry {entry} asks for keys and values twice")
                 seen_kv = True
-                kv_keys.setdefault((r.n_kv_heads, r.head_dim, r.window), []).append(entry)
+                kv_keys.setdefault((r.n_kv_heads, r.head_dim, r.window, r.v_head_dim or r.head_dim), []).append(entry)
             elif isinstance(r, StateRequest):
                 if r.dtype not in _TORCH:
                     raise CacheError(f"state '{r.name}': dtype {r.dtype} is not supported")
                 st_keys.setdefault((r.name, tuple(r.shape), r.dtype), []).append(entry)
             else:
                 raise CacheError(f"cache entry {entry}: unknown request {r!r}")
-    kv_groups = [KVGroupLayout(k[0], k[1], k[2], tuple(v)) for k, v in kv_keys.items()]
+    kv_groups = [KVGroupLayout(k[0], k[1], k[2], tuple(v), k[3]) for k, v in kv_keys.items()]
     st_groups = [StateGroupLayout(k[1], k[2], tuple(v), k[0]) for k, v in st_keys.items()]
     return kv_groups, st_groups
 
@@ -108,7 +109,7 @@ class SequenceCache:
             for g in self.kv_groups:
                 shape = (len(g.cache_entries), n_pages, g.n_kv_heads, page_size, g.head_dim)
                 self.k.append(torch.zeros(shape, dtype=kv_dtype, device=device))
-                self.v.append(torch.zeros(shape, dtype=kv_dtype, device=device))
+                self.v.append(torch.zeros(shape[:-1] + (g.v_head_dim or g.head_dim,), dtype=kv_dtype, device=device))
             for s in self.state_groups:
                 self.state.append(torch.zeros((len(s.cache_entries), max_slots) + tuple(s.shape),
                                               dtype=_TORCH[s.dtype], device=device))
@@ -133,7 +134,7 @@ class SequenceCache:
 
     def bytes_per_token(self) -> int:
         el = torch.empty((), dtype=self.kv_dtype).element_size()
-        return sum(2 * len(g.cache_entries) * g.n_kv_heads * g.head_dim * el for g in self.kv_groups)
+        return sum(len(g.cache_entries) * g.n_kv_heads * (g.head_dim + (g.v_head_dim or g.head_dim)) * el for g in self.kv_groups)
 
     # -- slots ---------------------------------------------------------------------------------
     def alloc_slot(self) -> int:

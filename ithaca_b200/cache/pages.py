@@ -68,6 +68,7 @@ class KVGroupLayout:
     head_dim: int
     window: Optional[int]            # None: every key is kept
     cache_entries: tuple             # cache entries (of the schedule) stored in this group, in order
+    v_head_dim: Optional[int] = None # size of a value head; None: as the key head
 
 
 @dataclass(frozen=True)

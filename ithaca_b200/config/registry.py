@@ -13,6 +13,7 @@ from typing import Any, Callable, Dict, Optional
 
 from .base import ConfigError, load_config_dict
 from .llama import LlamaConfig
+from .vebisun import VebisunConfig
 
 
 @dataclass(frozen=True)
@@ -50,8 +51,10 @@ def lookup_architecture(name: str) -> Architecture:
 
 def config_from_dict(d: Dict[str, Any]):
     archs = d.get("architectures")
+    if archs is None and isinstance(d.get("architecture"), str):
+        archs = [d["architecture"]]                       # some families name themselves with one string
     if not isinstance(archs, list) or not archs or not isinstance(archs[0], str):
-        raise ConfigError("config.json: 'architectures' must be a non-empty list of names")
+        raise ConfigError("config.json: 'architectures' must be a non-empty list of names (or 'architecture' one name)")
     arch = lookup_architecture(archs[0])
     return arch, arch.config_class.from_dict(d)
 
@@ -61,3 +64,4 @@ def config_from_model_dir(model_dir: str):
 
 
 register_architecture(LlamaConfig.ARCHITECTURE, LlamaConfig)
+register_architecture(VebisunConfig.ARCHITECTURE, VebisunConfig)

@@ -37,11 +37,12 @@ class PartSpec:
 class BlockSpec:
     """A layer: the arrangement ``kind`` (for instance ``"prenorm"``) and the
     parts it arranges.  ``position`` is handed to the mixer (rotary angles are
-    applied inside attention); ``None`` means the mixer sees no positions."""
+    applied inside attention); ``None`` means the mixer sees no positions.  A layer
+    without a feed-forward has ``feed_forward=None`` (arrangements that allow it say so)."""
 
     kind: str
     mixer: PartSpec
-    feed_forward: PartSpec
+    feed_forward: Optional[PartSpec]
     norms: Dict[str, PartSpec]
     position: Optional[PartSpec] = None
     params: Dict[str, Any] = field(default_factory=dict)
@@ -51,11 +52,15 @@ class BlockSpec:
 class ScheduleEntry:
     """One run of a layer.  ``layer`` indexes ``ModelSpec.layers`` (a layer may
     be named more than once).  ``cache`` is the cache entry the mixer works on;
-    ``writes_cache=False`` lets a run read a cache that an earlier run filled."""
+    ``writes_cache=False`` lets a run read a cache that an earlier run filled.
+    ``adds_input=True``: before this run the embedding's output (the residual stream
+    as it was before the first run) is added to the stream, as models do that send
+    the stream through the same layers several times."""
 
     layer: int
     cache: int
     writes_cache: bool = True
+    adds_input: bool = False
 
 
 @dataclass(frozen=True)
@@ -110,6 +115,7 @@ def describe(spec: ModelSpec) -> List[str]:
     out = []
     for n, e in enumerate(spec.schedule):
         b = spec.layers[e.layer]
-        out.append(f"run {n}: layer {e.layer} [{b.kind}: {b.mixer.kind} + {b.feed_forward.kind}] cache {e.cache}"
-                   + ("" if e.writes_cache else " (read only)"))
+        ff = b.feed_forward.kind if b.feed_forward is not None else "no feed-forward"
+        out.append(f"run {n}: layer {e.layer} [{b.kind}: {b.mixer.kind} + {ff}] cache {e.cache}"
+                   + ("" if e.writes_cache else " (read only)") + (" (input added first)" if e.adds_input else ""))
     return out

@@ -6,7 +6,8 @@
 // only on its position, not on how the tokens were cut into steps or batched.
 // Scores, the running maximum, the sum and the output are float; exp is the accurate
 // function.  This is the 32-bit path's attention and the fallback for head sizes the
-// tensor-core kernels do not take.
+// tensor-core kernels do not take.  Options: a cap on the scores, s <- cap * tanh(s / cap) after the scale
+// (cap 0 = none), and value heads of another size than the key heads (hdv).
 #include <math.h>
 #define IK_FAMILY 4
 #include "common.cuh"
@@ -20,12 +21,12 @@ template <typename TQ, typename TC, typename TO>
 __global__ void __launch_bounds__(TILE)
 attention_simt_kernel(const TQ* __restrict__ q, const TC* __restrict__ k_pages, const TC* __restrict__ v_pages,
                       TO* __restrict__ out, const int* __restrict__ token_seq, const int* __restrict__ token_pos,
-                      const int* __restrict__ table, int table_stride, int nh, int nkv, int hd, float scale,
-                      int window, int page_size, int n_pages, int* status) {
+                      const int* __restrict__ table, int table_stride, int nh, int nkv, int hd, int hdv, float scale,
+                      float softcap, int window, int page_size, int n_pages, int* status) {
     ik_pdl_wait();
     ik_pdl_launch_dependents();
     extern __shared__ __align__(16) unsigned char smem[];
-    size_t* row = (size_t*)smem;              // [TILE] element offset of key j's row in the pages
+    size_t* row = (size_t*)smem;              // [TILE] row of key j in the pages (page, kv head, place), times the head size = its offset
     float* qs = (float*)(row + TILE);         // [hd]
     float* sc = qs + hd;                      // [TILE]
     float* red = sc + TILE;                   // [32]
@@ -54,12 +55,13 @@ attention_simt_kernel(const TQ* __restrict__ q, const TC* __restrict__ k_pages, 
                 ik_set_status(status, IK_STATUS_READ_NO_PAGE);
                 off = 0;
             } else {
-                off = (((size_t)page * nkv + kvh) * page_size + (j % page_size)) * hd;
+                off = ((size_t)page * nkv + kvh) * page_size + (j % page_size);
             }
-            const TC* kr = k_pages + off;
+            const TC* kr = k_pages + off * hd;
             float dot = 0.f;
             for (int i = 0; i < hd; i++) dot = fmaf(qs[i], ik_ld(kr, i), dot);
             s = dot * scale;
+            if (softcap > 0.f) s = softcap * tanhf(s / softcap);
         }
         row[tid] = off;
         const float tile_max = ik_block_max<TILE>(s, red);
@@ -73,11 +75,11 @@ attention_simt_kernel(const TQ* __restrict__ q, const TC* __restrict__ k_pages, 
         #pragma unroll
         for (int r = 0; r < MAX_R; r++) {
             const int i = tid + r * TILE;
-            if (i < hd) {
+            if (i < hdv) {
                 float acc = o[r] * alpha;
                 for (int jj = 0; jj < n_in_tile; jj++) {
                     const float pj = sc[jj];
-                    if (pj != 0.f) acc = fmaf(pj, ik_ld(v_pages + row[jj], i), acc);
+                    if (pj != 0.f) acc = fmaf(pj, ik_ld(v_pages + row[jj] * hdv, i), acc);
                 }
                 o[r] = acc;
             }
@@ -85,12 +87,12 @@ attention_simt_kernel(const TQ* __restrict__ q, const TC* __restrict__ k_pages, 
         m = m_new;
         __syncthreads();                                       // sc[] and row[] are rewritten by the next tile
     }
-    TO* orow = out + ((size_t)t * nh + h) * hd;
+    TO* orow = out + ((size_t)t * nh + h) * hdv;
     const float inv = 1.0f / l;
     #pragma unroll
     for (int r = 0; r < MAX_R; r++) {
         const int i = tid + r * TILE;
-        if (i < hd) ik_st(orow, i, o[r] * inv);
+        if (i < hdv) ik_st(orow, i, o[r] * inv);
     }
 }
 
@@ -98,16 +100,16 @@ attention_simt_kernel(const TQ* __restrict__ q, const TC* __restrict__ k_pages, 
 
 IK_EXPORT int ik_attention_simt(const void* q, int q_dtype, const void* k_pages, const void* v_pages, int cache_dtype,
                                 void* out, int out_dtype, const int* token_seq, const int* token_pos, const int* table,
-                                int table_stride, int T, int nh, int nkv, int hd, float scale, int window,
+                                int table_stride, int T, int nh, int nkv, int hd, int hdv, float scale, float softcap, int window,
                                 int page_size, int n_pages, int* status, cudaStream_t stream) {
-    if (T < 0 || nh <= 0 || nkv <= 0 || nh % nkv || hd <= 0 || hd > TILE * MAX_R || page_size <= 0) return IK_BAD_ARGUMENT;
+    if (T < 0 || nh <= 0 || nkv <= 0 || nh % nkv || hd <= 0 || hdv <= 0 || hdv > TILE * MAX_R || page_size <= 0 || softcap < 0.f) return IK_BAD_ARGUMENT;
     if (q_dtype != out_dtype) return IK_BAD_ARGUMENT;
     if (T == 0) return IK_OK;
     dim3 grid(T, nh);
     const size_t smem = (size_t)(hd + TILE + 32) * sizeof(float) + TILE * sizeof(size_t);
 #define IK_ATT(TQ, TC)                                                                                                \
     IK_RETURN_IF_ERROR(ik_launch(attention_simt_kernel<TQ, TC, TQ>, grid, TILE, smem, stream, (const TQ*)q, (const TC*)k_pages, (const TC*)v_pages, \
-        (TQ*)out, token_seq, token_pos, table, table_stride, nh, nkv, hd, scale, window, page_size, n_pages, status))
+        (TQ*)out, token_seq, token_pos, table, table_stride, nh, nkv, hd, hdv, scale, softcap, window, page_size, n_pages, status))
     if (q_dtype == IK_F32 && cache_dtype == IK_F32) IK_ATT(float, float);
     else if (q_dtype == IK_BF16 && cache_dtype == IK_BF16) IK_ATT(__nv_bfloat16, __nv_bfloat16);
     else if (q_dtype == IK_F32 && cache_dtype == IK_BF16) IK_ATT(float, __nv_bfloat16);

@@ -1,0 +1,283 @@
+// Mixture of experts: routing, the grouping of (token, choice) pairs by expert, the experts' products
+// over those groups, and the weighted sum of a token's choices.
+//
+//   route     scores = softmax(router logits) over all experts (float).  Experts form `n_groups` equal groups of
+//             neighbours; a group counts by its best score, only experts of the `keep` best groups can be chosen
+//             (n_groups <= 1: all can), and the `top` best of them are.  The weights are the chosen experts' scores as
+//             they are, or divided by their sum (renorm).  Equal scores: the lower index wins.
+//   sort      a counting sort of the A = T * top assignments by expert: sorted[] lists assignment ids (t * top + k)
+//             expert by expert; tiles[] cuts every expert's run into row tiles of MOE_BM for the products.
+//   gemm      for every row tile, rows of X (chosen through `sorted`) times the tile's expert's matrix.  Mode 0:
+//             X = the tokens' activations (row a / top), W = [gate; up] of the expert, result h = silu(g) * u at the
+//             sorted place.  Mode 1: X = h at the sorted place, W = down, result at the assignment's own row a.
+//             CUDA cores, float accumulation in ascending k per output element: a row's result does not depend on
+//             its place in a tile nor on what else is in the step.
+//   combine   y[t] = sum_k weight[t, k] * out[t * top + k], ascending k.
+#include <math.h>
+#define IK_FAMILY 2
+#include "common.cuh"
+
+namespace {
+
+constexpr int MOE_BM = 64, MOE_BN = 64, MOE_BK = 16, MOE_TM = 4, MOE_TN = 4;
+
+// ------------------------------------------------------------------------------------------ route
+// One warp per token.  smem: scores [E] then group bests [n_groups] per warp.
+__global__ void __launch_bounds__(128)
+moe_route_kernel(const float* __restrict__ logits, int* __restrict__ chosen, float* __restrict__ weight, int T, int E,
+                 int top, int n_groups, int keep, int renorm) {
+    ik_pdl_wait();
+    IK_AFTER_WAIT(logits);
+    ik_pdl_launch_dependents();
+    extern __shared__ float sm[];
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int t = blockIdx.x * 4 + warp;
+    if (t >= T) return;
+    const int ng = n_groups > 1 ? n_groups : 0;
+    float* sc = sm + (size_t)warp * (E + ng);
+    float* gb = sc + E;
+    const float* z = logits + (size_t)t * E;
+    float m = -INFINITY;
+    for (int e = lane; e < E; e += 32) m = fmaxf(m, z[e]);
+    for (int o = 16; o > 0; o >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, o));
+    float sum = 0.f;
+    for (int e = lane; e < E; e += 32) { const float p = expf(z[e] - m); sc[e] = p; sum += p; }
+    for (int o = 16; o > 0; o >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, o);
+    const float inv = 1.0f / sum;
+    for (int e = lane; e < E; e += 32) sc[e] *= inv;
+    __syncwarp();
+    // warp-wide argmax over n values v(i) >= 0 (taken ones are marked -1); the lower index wins a tie
+    auto argmax = [&](const float* v, int n) -> int {
+        float bv = -2.f; int bi = 0x7fffffff;
+        for (int i = lane; i < n; i += 32) if (v[i] > bv) { bv = v[i]; bi = i; }
+        for (int o = 16; o > 0; o >>= 1) {
+            const float ov = __shfl_xor_sync(0xffffffffu, bv, o);
+            const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
+            if (ov > bv || (ov == bv && oi < bi)) { bv = ov; bi = oi; }
+        }
+        return bi;
+    };
+    if (ng) {
+        const int per = E / ng;
+        for (int g = lane; g < ng; g += 32) {
+            float b = -1.f;
+            for (int i = 0; i < per; i++) b = fmaxf(b, sc[g * per + i]);
+            gb[g] = b;
+        }
+        __syncwarp();
+        // groups that are kept are marked by -1; then the others' experts are struck out
+        for (int k = 0; k < keep; k++) {
+            const int g = argmax(gb, ng);
+            if (lane == 0) gb[g] = -1.f;
+            __syncwarp();
+        }
+        for (int e = lane; e < E; e += 32) if (gb[e / per] != -1.f) sc[e] = -(sc[e] + 2.f);     // struck out, score kept: -(s + 2) <= -2
+        __syncwarp();
+    }
+    float wsum = 0.f;
+    for (int k = 0; k < top; k++) {
+        const int e = argmax(sc, E);
+        const float s = sc[e];
+        wsum += s;
+        __syncwarp();
+        if (lane == 0) { chosen[(size_t)t * top + k] = e; weight[(size_t)t * top + k] = s; sc[e] = -1.f; }
+        __syncwarp();
+    }
+    if (renorm && lane == 0) for (int k = 0; k < top; k++) weight[(size_t)t * top + k] /= wsum;
+}
+
+// ------------------------------------------------------------------------------------------ sort
+// One block.  offsets [E + 1], sorted [A], tiles [max_tiles][2] = (expert, first sorted place), n_tiles [1].
+__global__ void __launch_bounds__(1024)
+moe_sort_kernel(const int* __restrict__ chosen, int* __restrict__ offsets, int* __restrict__ sorted, int* __restrict__ tiles,
+                int* __restrict__ n_tiles, int A, int E, int max_tiles) {
+    ik_pdl_wait();
+    IK_AFTER_WAIT(chosen);
+    ik_pdl_launch_dependents();
+    extern __shared__ int cnt[];         // [E] counts, then [E] cursors
+    int* cur = cnt + E;
+    for (int e = threadIdx.x; e < E; e += blockDim.x) cnt[e] = 0;
+    __syncthreads();
+    for (int a = threadIdx.x; a < A; a += blockDim.x) {
+        const int e = chosen[a];
+        if (e >= 0 && e < E) atomicAdd(&cnt[e], 1);
+    }
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        int at = 0, nt = 0;
+        for (int e = 0; e < E; e++) {
+            offsets[e] = at;
+            cur[e] = at;
+            for (int r = 0; r < cnt[e] && nt < max_tiles; r += MOE_BM) { tiles[2 * nt] = e; tiles[2 * nt + 1] = at + r; nt++; }
+            at += cnt[e];
+        }
+        offsets[E] = at;
+        *n_tiles = nt;
+    }
+    __syncthreads();
+    for (int a = threadIdx.x; a < A; a += blockDim.x) {
+        const int e = chosen[a];
+        if (e >= 0 && e < E) sorted[atomicAdd(&cur[e], 1)] = a;
+    }
+}
+
+// ------------------------------------------------------------------------------------------ products
+template <typename TX, typename TW, typename TY, int MODE>
+__global__ void __launch_bounds__(256)
+moe_gemm_kernel(const TX* __restrict__ X, const TW* __restrict__ W, TY* __restrict__ Y, const int* __restrict__ offsets,
+                const int* __restrict__ sorted, const int* __restrict__ tiles, const int* __restrict__ n_tiles, int top,
+                int N, int K, int ldx, int ldy) {
+    ik_pdl_wait();
+    IK_AFTER_WAIT(X);
+    IK_AFTER_WAIT(offsets);
+    IK_AFTER_WAIT(sorted);
+    IK_AFTER_WAIT(tiles);
+    IK_AFTER_WAIT(n_tiles);
+    ik_pdl_launch_dependents();
+    if ((int)blockIdx.y >= *n_tiles) return;
+    constexpr int NW = MODE == 0 ? 2 : 1;                  // mode 0 carries gate and up of the same columns
+    __shared__ float xs[MOE_BK][MOE_BM + 1];
+    __shared__ float ws[NW][MOE_BK][MOE_BN + 1];
+    __shared__ int src_row[MOE_BM], dst_row[MOE_BM];
+    const int e = tiles[2 * blockIdx.y], p0 = tiles[2 * blockIdx.y + 1];
+    const int rows = min(MOE_BM, offsets[e + 1] - p0);
+    const int n0 = blockIdx.x * MOE_BN;
+    // expert e's matrix: mode 0 [2N, K] (gate rows, then up rows), mode 1 [N, K]
+    const TW* We = W + (size_t)e * (MODE == 0 ? 2 : 1) * N * K;
+    if (threadIdx.x < MOE_BM) {
+        const int r = threadIdx.x;
+        const int a = r < rows ? sorted[p0 + r] : -1;
+        src_row[r] = a < 0 ? -1 : (MODE == 0 ? a / top : p0 + r);
+        dst_row[r] = a < 0 ? -1 : (MODE == 0 ? p0 + r : a);
+    }
+    __syncthreads();
+    const int tx = threadIdx.x % 16, ty = threadIdx.x / 16;
+    float acc[NW][MOE_TM][MOE_TN];
+    #pragma unroll
+    for (int w = 0; w < NW; w++)
+        #pragma unroll
+        for (int i = 0; i < MOE_TM; i++)
+            #pragma unroll
+            for (int j = 0; j < MOE_TN; j++) acc[w][i][j] = 0.f;
+    for (int k0 = 0; k0 < K; k0 += MOE_BK) {
+        #pragma unroll
+        for (int l = 0; l < 4; l++) {
+            const int idx = threadIdx.x + l * 256;
+            const int r = idx / MOE_BK, c = idx % MOE_BK, k = k0 + c;
+            const int sr = src_row[r];
+            xs[c][r] = (sr >= 0 && k < K) ? ik_ld(X, (size_t)sr * ldx + k) : 0.f;
+            #pragma unroll
+            for (int w = 0; w < NW; w++)
+                ws[w][c][r] = (n0 + r < N && k < K) ? ik_ld(We, ((size_t)w * N + n0 + r) * K + k) : 0.f;
+        }
+        __syncthreads();
+        #pragma unroll
+        for (int kk = 0; kk < MOE_BK; kk++) {
+            float a[MOE_TM];
+            #pragma unroll
+            for (int i = 0; i < MOE_TM; i++) a[i] = xs[kk][ty * MOE_TM + i];
+            #pragma unroll
+            for (int w = 0; w < NW; w++) {
+                float b[MOE_TN];
+                #pragma unroll
+                for (int j = 0; j < MOE_TN; j++) b[j] = ws[w][kk][tx + 16 * j];
+                #pragma unroll
+                for (int i = 0; i < MOE_TM; i++)
+                    #pragma unroll
+                    for (int j = 0; j < MOE_TN; j++) acc[w][i][j] = fmaf(a[i], b[j], acc[w][i][j]);
+            }
+        }
+        __syncthreads();
+    }
+    #pragma unroll
+    for (int i = 0; i < MOE_TM; i++) {
+        const int dr = dst_row[ty * MOE_TM + i];
+        if (dr < 0) continue;
+        #pragma unroll
+        for (int j = 0; j < MOE_TN; j++) {
+            const int n = n0 + tx + 16 * j;
+            if (n >= N) continue;
+            const float v = MODE == 0 ? ik_swiglu(acc[0][i][j], acc[NW - 1][i][j]) : acc[0][i][j];
+            ik_st(Y, (size_t)dr * ldy + n, v);
+        }
+    }
+}
+
+// ------------------------------------------------------------------------------------------ combine
+__global__ void moe_combine_kernel(const float* __restrict__ parts, const float* __restrict__ weight, float* __restrict__ y,
+                                   int T, int top, int d) {
+    ik_pdl_wait();
+    IK_AFTER_WAIT(parts);
+    IK_AFTER_WAIT(weight);
+    ik_pdl_launch_dependents();
+    const size_t total = (size_t)T * d, stride = (size_t)gridDim.x * blockDim.x;
+    for (size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x; idx < total; idx += stride) {
+        const size_t t = idx / d;
+        const int i = (int)(idx - t * d);
+        float acc = 0.f;
+        for (int k = 0; k < top; k++) acc = fmaf(weight[t * top + k], parts[(t * top + k) * d + i], acc);
+        y[idx] = acc;
+    }
+}
+
+template <int MODE>
+int launch_gemm(const void* X, int x_dtype, const void* W, int w_dtype, void* Y, int y_dtype, const int* offsets,
+                const int* sorted, const int* tiles, const int* n_tiles, int max_tiles, int top, int N, int K, int ldx,
+                int ldy, cudaStream_t stream) {
+    dim3 grid((N + MOE_BN - 1) / MOE_BN, max_tiles);
+#define IK_MOE(TX, TW, TY) \
+    IK_RETURN_IF_ERROR(ik_launch(moe_gemm_kernel<TX, TW, TY, MODE>, grid, 256, 0, stream, (const TX*)X, (const TW*)W, (TY*)Y, offsets, sorted, tiles, n_tiles, top, N, K, ldx, ldy))
+    const int code = x_dtype * 4 + w_dtype * 2 + y_dtype;
+    switch (code) {
+        case 0: IK_MOE(float, float, float); break;
+        case 2: IK_MOE(float, __nv_bfloat16, float); break;
+        case 6: IK_MOE(__nv_bfloat16, __nv_bfloat16, float); break;
+        case 7: IK_MOE(__nv_bfloat16, __nv_bfloat16, __nv_bfloat16); break;
+        default: return IK_UNSUPPORTED;
+    }
+#undef IK_MOE
+    IK_LAUNCH_STATUS();
+}
+
+}  // namespace
+
+IK_EXPORT int ik_moe_tile_rows() { return MOE_BM; }
+
+IK_EXPORT int ik_moe_route(const float* logits, int* chosen, float* weight, int T, int E, int top, int n_groups, int keep,
+                           int renorm, cudaStream_t stream) {
+    if (T < 0 || E <= 0 || top <= 0 || top > E) return IK_BAD_ARGUMENT;
+    if (n_groups > 1 && (E % n_groups || keep <= 0 || keep > n_groups || top > keep * (E / n_groups))) return IK_BAD_ARGUMENT;
+    if (T == 0) return IK_OK;
+    const size_t smem = 4 * (size_t)(E + (n_groups > 1 ? n_groups : 0)) * sizeof(float);
+    if (smem > 48 * 1024) return IK_UNSUPPORTED;
+    IK_RETURN_IF_ERROR(ik_launch(moe_route_kernel, (T + 3) / 4, 128, smem, stream, logits, chosen, weight, T, E, top, n_groups, keep, renorm));
+    IK_LAUNCH_STATUS();
+}
+
+IK_EXPORT int ik_moe_sort(const int* chosen, int* offsets, int* sorted, int* tiles, int* n_tiles, int A, int E, int max_tiles,
+                          cudaStream_t stream) {
+    if (A < 0 || E <= 0 || max_tiles < 0) return IK_BAD_ARGUMENT;
+    if ((size_t)2 * E * sizeof(int) > 48 * 1024) return IK_UNSUPPORTED;
+    IK_RETURN_IF_ERROR(ik_launch(moe_sort_kernel, 1, 1024, (size_t)2 * E * sizeof(int), stream, chosen, offsets, sorted, tiles, n_tiles, A, E, max_tiles));
+    IK_LAUNCH_STATUS();
+}
+
+// mode 0: X [T, K] tokens, W [E, 2N, K], Y [A, N] = silu(gate) * up at sorted places.  mode 1: X [A, K] at sorted
+// places, W [E, N, K], Y [A, N] at the assignments' rows.
+IK_EXPORT int ik_moe_gemm(int mode, const void* X, int x_dtype, const void* W, int w_dtype, void* Y, int y_dtype,
+                          const int* offsets, const int* sorted, const int* tiles, const int* n_tiles, int max_tiles, int top,
+                          int N, int K, int ldx, int ldy, cudaStream_t stream) {
+    if (max_tiles < 0 || top <= 0 || N <= 0 || K <= 0 || ldx < K || ldy < N || max_tiles > 65535) return IK_BAD_ARGUMENT;
+    if (max_tiles == 0) return IK_OK;
+    if (mode == 0) return launch_gemm<0>(X, x_dtype, W, w_dtype, Y, y_dtype, offsets, sorted, tiles, n_tiles, max_tiles, top, N, K, ldx, ldy, stream);
+    if (mode == 1) return launch_gemm<1>(X, x_dtype, W, w_dtype, Y, y_dtype, offsets, sorted, tiles, n_tiles, max_tiles, top, N, K, ldx, ldy, stream);
+    return IK_BAD_ARGUMENT;
+}
+
+IK_EXPORT int ik_moe_combine(const float* parts, const float* weight, float* y, int T, int top, int d, cudaStream_t stream) {
+    if (T < 0 || top <= 0 || d <= 0) return IK_BAD_ARGUMENT;
+    if (T == 0) return IK_OK;
+    const size_t total = (size_t)T * d, want = (total + 255) / 256, cap = (size_t)ik_sm_count() * 16;
+    IK_RETURN_IF_ERROR(ik_launch(moe_combine_kernel, (int)(want < cap ? want : cap), 256, 0, stream, parts, weight, y, T, top, d));
+    IK_LAUNCH_STATUS();
+}

@@ -84,7 +84,16 @@ _SIGNATURES = {
     "ik_rope_table": [_vp, _vp, _vp, _i, _i, _vp],
     "ik_gemm_qkv_rope_mma": [_vp, _vp, _i, _i, _i, _i, _i, _vp, _vp],
     "ik_gemm_qkv_rope_tcgen05": [_vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _vp, _vp, _vp],
-    "ik_attention_simt": [_vp, _i, _vp, _vp, _i, _vp, _i, _vp, _vp, _vp, _i, _i, _i, _i, _i, _f, _i, _i, _i, _vp, _vp],
+    "ik_attention_simt": [_vp, _i, _vp, _vp, _i, _vp, _i, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _f, _f, _i, _i, _i, _vp, _vp],
+    "ik_layernorm": [_vp, _vp, _vp, _vp, _vp, _i, _vp, _f, _i, _i, _f, _vp],
+    "ik_add": [_vp, _vp, _u64, _vp],
+    "ik_conv_rope_append": [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _vp, _vp, _i, _vp, _vp, _vp, _i, _vp, _i, _i, _i, _i, _i, _i, _i,
+                            _i, _i, _i, _i, _i, _vp, _vp],
+    "ik_moe_tile_rows": [],
+    "ik_moe_route": [_vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _vp],
+    "ik_moe_sort": [_vp, _vp, _vp, _vp, _vp, _i, _i, _i, _vp],
+    "ik_moe_gemm": [_i, _vp, _i, _vp, _i, _vp, _i, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _vp],
+    "ik_moe_combine": [_vp, _vp, _vp, _i, _i, _i, _vp],
     "ik_argmax": [_vp, _i, _vp, _i, _i, _vp, _vp],
     "ik_argmax_scratch_bytes": [],
     "ik_selftest_wait_expires": [_vp, _vp, _vp, _u64, _vp],
@@ -548,22 +557,170 @@ def gemm_qkv_rope(x: torch.Tensor, w: torch.Tensor, q_out: torch.Tensor, k_pages
 
 def attention_simt(q: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Tensor, token_seq: torch.Tensor,
                    token_pos: torch.Tensor, table: torch.Tensor, n_heads: int, scale: float, window: int,
-                   status: Optional[torch.Tensor], out: Optional[torch.Tensor] = None) -> torch.Tensor:
+                   status: Optional[torch.Tensor], out: Optional[torch.Tensor] = None, softcap: float = 0.0) -> torch.Tensor:
+    """``softcap``: scores become cap * tanh(score / cap) after the scale (0 = no cap).  The value pages may
+    have a head size of their own; the output is then [T, n_heads * that size]."""
     _need(q, "q")
     _need(k_pages, "k_pages")
     _need(v_pages, "v_pages")
     _need(table, "table", torch.int32)
     n_pages, nkv, page_size, hd = k_pages.shape
+    hdv = v_pages.shape[3]
     T = q.shape[0]
-    if q.shape[1] != n_heads * hd:
-        raise KernelError("attention: q has the wrong width")
+    if q.shape[1] != n_heads * hd or v_pages.shape[:3] != k_pages.shape[:3] or v_pages.dtype != k_pages.dtype:
+        raise KernelError("attention: q or the value pages have the wrong shape")
     if out is None:
-        out = torch.empty_like(q)
+        out = torch.empty((T, n_heads * hdv), dtype=q.dtype, device=q.device)
     _work(f"attention_simt {T}x{n_heads}", _nbytes(q, out))
     _check(lib().ik_attention_simt(_ptr(q), _code(q), _ptr(k_pages), _ptr(v_pages), _code(k_pages), _ptr(out),
                                    _code(out), _ptr(token_seq), _ptr(token_pos), _ptr(table), table.stride(0), T,
-                                   n_heads, nkv, hd, scale, window, page_size, n_pages, _ptr(status), _stream()),
+                                   n_heads, nkv, hd, hdv, scale, softcap, window, page_size, n_pages, _ptr(status), _stream()),
            "attention_simt")
+    return out
+
+
+def layernorm(x: torch.Tensor, weight: torch.Tensor, bias: torch.Tensor, eps: float, out_dtype: torch.dtype,
+              rows_in: Optional[torch.Tensor] = None, into: Optional[torch.Tensor] = None, mult: float = 1.0) -> torch.Tensor:
+    """y = (x - mean) / sqrt(var + eps) * weight + bias per row, in float.  Returns y in ``out_dtype``, or, when
+    ``into`` (float, the shape of x) is given, adds ``mult * y`` to it and returns it."""
+    _need(x, "x", torch.float32)
+    _need(weight, "weight", torch.float32)
+    _need(bias, "bias", torch.float32)
+    d = x.shape[-1]
+    if weight.numel() != d or bias.numel() != d:
+        raise KernelError(f"layernorm: weight and bias need {d} elements")
+    rows = x.numel() // d if rows_in is None else rows_in.numel()
+    if rows_in is not None:
+        _need(rows_in, "rows_in", torch.int32)
+    out = None
+    if into is not None:
+        _need(into, "into", torch.float32)
+        if into.shape != x.shape or rows_in is not None:
+            raise KernelError("layernorm: the stream to add to must have the input's shape")
+    else:
+        out = torch.empty((rows, d), dtype=out_dtype, device=x.device)
+    _work(f"layernorm{' +add' if into is not None else ''} {rows}x{d}", rows * d * (12 if into is not None else 4 + out.element_size()))
+    _check(lib().ik_layernorm(_ptr(x), _ptr(rows_in), _ptr(weight), _ptr(bias), _ptr(out), _code(out) if out is not None else F32,
+                              _ptr(into), mult, rows, d, eps, _stream()), "layernorm")
+    return into if into is not None else out
+
+
+def add_(y: torch.Tensor, x: torch.Tensor) -> torch.Tensor:
+    """y += x (float, equal shapes)."""
+    _need(y, "y", torch.float32)
+    _need(x, "x", torch.float32)
+    if y.shape != x.shape:
+        raise KernelError("add: shapes differ")
+    _work(f"add {y.numel()}", 12 * y.numel())
+    _check(lib().ik_add(_ptr(y), _ptr(x), y.numel(), _stream()), "add")
+    return y
+
+
+def conv_rope_append(qkv: torch.Tensor, conv_w: Optional[torch.Tensor], ring: Optional[torch.Tensor], slots: torch.Tensor,
+                     cu_seqlens: torch.Tensor, kv_lens: torch.Tensor, q_out: torch.Tensor, k_pages: torch.Tensor,
+                     v_pages: torch.Tensor, token_seq: torch.Tensor, token_pos: torch.Tensor, table: torch.Tensor,
+                     inv_freq: Optional[torch.Tensor], n_heads: int, n_kv_heads: int, rotary_dim: int, pairing: int,
+                     write_cache: bool, status: Optional[torch.Tensor]) -> None:
+    """Short causal convolution over time on the projected q, k, v (``conv_w`` [channels, taps]; None = no
+    convolution), rotary encoding of q and k, append of k and v to the pages.  ``ring`` [max_slots, taps, channels]
+    holds each sequence's last projected values and is brought up to date."""
+    _need(qkv, "qkv", torch.float32)
+    _need(q_out, "q_out")
+    _need(k_pages, "k_pages")
+    _need(v_pages, "v_pages")
+    _need(table, "table", torch.int32)
+    n_pages, nkv, page_size, hd = k_pages.shape
+    hdv = v_pages.shape[3]
+    T, ctot = qkv.shape
+    taps = 0
+    if conv_w is not None:
+        _need(conv_w, "conv_w", torch.float32)
+        taps = conv_w.shape[1]
+        if conv_w.shape[0] != ctot:
+            raise KernelError("conv_rope_append: one row of taps per channel is needed")
+        if taps > 1:
+            _need(ring, "ring", torch.float32)
+            if tuple(ring.shape[1:]) != (taps, ctot):
+                raise KernelError("conv_rope_append: the ring has the wrong shape")
+    if nkv != n_kv_heads or ctot != (n_heads + nkv) * hd + nkv * hdv or v_pages.shape[:3] != k_pages.shape[:3] \
+            or v_pages.dtype != k_pages.dtype or q_out.shape != (T, n_heads * hd):
+        raise KernelError("conv_rope_append: the sizes do not fit together")
+    _work(f"conv_rope_append {T}", _nbytes(qkv, q_out) + T * nkv * (hd + hdv) * k_pages.element_size())
+    _check(lib().ik_conv_rope_append(_ptr(qkv), _ptr(conv_w), _ptr(ring) if taps > 1 else 0, _ptr(slots), _ptr(cu_seqlens),
+                                     _ptr(kv_lens), _ptr(q_out), _code(q_out), _ptr(k_pages), _ptr(v_pages), _code(k_pages),
+                                     _ptr(token_seq), _ptr(token_pos), _ptr(table), table.stride(0), _ptr(inv_freq), T,
+                                     slots.numel(), n_heads, nkv, hd, hdv, rotary_dim, pairing, taps, page_size, n_pages,
+                                     1 if write_cache else 0, _ptr(status), _stream()), "conv_rope_append", kernels=2 if taps > 1 else 1)
+
+
+def moe_route(logits: torch.Tensor, top: int, n_groups: int = 0, keep: int = 0, renorm: bool = False):
+    """Softmax scores over the experts and the ``top`` best among the ``keep`` best of ``n_groups`` groups of
+    neighbours (0 groups: among all).  Returns (chosen int32 [T, top], weights float [T, top])."""
+    _need(logits, "logits", torch.float32)
+    T, E = logits.shape
+    chosen = torch.empty((T, top), dtype=torch.int32, device=logits.device)
+    weight = torch.empty((T, top), dtype=torch.float32, device=logits.device)
+    _work(f"moe_route {T}x{E}", _nbytes(logits, chosen, weight))
+    _check(lib().ik_moe_route(_ptr(logits), _ptr(chosen), _ptr(weight), T, E, top, n_groups, keep, 1 if renorm else 0, _stream()),
+           "moe_route")
+    return chosen, weight
+
+
+class MoEPlan:
+    """Where a step's (token, choice) pairs sit once grouped by expert: device arrays only."""
+    __slots__ = ("offsets", "sorted", "tiles", "n_tiles", "max_tiles", "top", "n_assign", "n_experts")
+
+
+def moe_sort(chosen: torch.Tensor, n_experts: int) -> MoEPlan:
+    _need(chosen, "chosen", torch.int32)
+    T, top = chosen.shape
+    A = T * top
+    bm = lib().ik_moe_tile_rows()
+    p = MoEPlan()
+    p.top, p.n_assign, p.n_experts = top, A, n_experts
+    p.max_tiles = min(A, A // bm + n_experts)
+    meta = torch.empty(n_experts + 1 + A + 2 * p.max_tiles + 1, dtype=torch.int32, device=chosen.device)
+    p.offsets = meta[:n_experts + 1]
+    p.sorted = meta[n_experts + 1:n_experts + 1 + A]
+    p.tiles = meta[n_experts + 1 + A:n_experts + 1 + A + 2 * p.max_tiles]
+    p.n_tiles = meta[n_experts + 1 + A + 2 * p.max_tiles:]
+    _work(f"moe_sort {A}", 8 * A)
+    _check(lib().ik_moe_sort(_ptr(chosen), _ptr(p.offsets), _ptr(p.sorted), _ptr(p.tiles), _ptr(p.n_tiles), A, n_experts,
+                             p.max_tiles, _stream()), "moe_sort")
+    return p
+
+
+def moe_gemm(mode: int, x: torch.Tensor, w: torch.Tensor, plan: MoEPlan, out_dtype: torch.dtype) -> torch.Tensor:
+    """Mode 0: ``x`` [T, d] tokens, ``w`` [E, 2 ff, d] (gate rows then up rows) -> silu(gate) * up [A, ff] in sorted
+    order.  Mode 1: ``x`` [A, ff] in sorted order, ``w`` [E, d, ff] -> [A, d], row t * top + k for token t's choice k."""
+    _need(x, "x")
+    _need(w, "w")
+    E, rows, K = w.shape
+    N = rows // 2 if mode == 0 else rows
+    if x.shape[1] != K or E != plan.n_experts:
+        raise KernelError("moe_gemm: the sizes do not fit together")
+    out = torch.empty((plan.n_assign, N), dtype=out_dtype, device=x.device)
+    A = plan.n_assign
+    _work(f"moe_gemm{mode} {A}x{rows}x{K}", A * K * x.element_size() + min(E, A) * rows * K * w.element_size() + A * N * out.element_size(),
+          2 * A * rows * K)
+    _check(lib().ik_moe_gemm(mode, _ptr(x), _code(x), _ptr(w), _code(w), _ptr(out), _code(out), _ptr(plan.offsets),
+                             _ptr(plan.sorted), _ptr(plan.tiles), _ptr(plan.n_tiles), plan.max_tiles, plan.top, N, K,
+                             x.stride(0), out.stride(0), _stream()), "moe_gemm")
+    return out
+
+
+def moe_combine(parts: torch.Tensor, weight: torch.Tensor, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """y[t] = sum_k weight[t, k] * parts[t * top + k]."""
+    _need(parts, "parts", torch.float32)
+    _need(weight, "weight", torch.float32)
+    T, top = weight.shape
+    d = parts.shape[1]
+    if parts.shape[0] != T * top:
+        raise KernelError("moe_combine: one row per (token, choice) is needed")
+    if out is None:
+        out = torch.empty((T, d), dtype=torch.float32, device=parts.device)
+    _work(f"moe_combine {T}x{d}", _nbytes(parts, out))
+    _check(lib().ik_moe_combine(_ptr(parts), _ptr(weight), _ptr(out), T, top, d, _stream()), "moe_combine")
     return out
 
 

@@ -15,6 +15,7 @@ import torch
 from ..cache.cache import SequenceCache
 from ..config import ConfigError, config_from_model_dir
 from ..config.spec import ModelSpec, validate_schedule
+from ..csrc import ops
 from ..parts import BLOCKS, EMBEDDINGS, HEADS, NORMS, Runtime
 from ..parts.block import _merge
 from ..weights.loader import TensorReq, WeightError, check_tensors, load_checkpoint, read_model_tensors, _storage_form
@@ -40,7 +41,8 @@ def streamed_tensor_names(spec: ModelSpec) -> List[str]:
         b = spec.layers[e.layer]
         from ..parts import FEED_FORWARDS, MIXERS
         for part, reg in ((b.mixer, MIXERS), (b.feed_forward, FEED_FORWARDS)):
-            names += list(reg.get(part.kind).manifest(part))
+            if part is not None:
+                names += list(reg.get(part.kind).manifest(part))
     names += list(HEADS.get(spec.head.kind).manifest(spec.head))
     return list(dict.fromkeys(names))
 
@@ -71,8 +73,8 @@ class DecoderModel:
         """True when every mixer and feed-forward says that a captured step may be replayed for
         other slots and positions (they read those from the step's device arrays, never from
         host values).  A part that does not say so is stepped eagerly."""
-        return all(getattr(l.mixer, "graph_safe", False) and getattr(l.feed_forward, "graph_safe", False)
-                   for l in self.layers)
+        return all(getattr(l.mixer, "graph_safe", False)
+                   and (l.feed_forward is None or getattr(l.feed_forward, "graph_safe", False)) for l in self.layers)
 
     def cache_requests(self) -> Dict[int, List[object]]:
         out: Dict[int, List[object]] = {}
@@ -85,7 +87,10 @@ class DecoderModel:
         """Runs the step's tokens through every scheduled run; returns float32 logits
         [wanted rows, vocab], or None when no row is wanted."""
         h = self.embedding.forward(ctx.token_ids, ctx)
+        h0 = h.clone() if any(e.adds_input for e in self.spec.schedule) else None
         for e in self.spec.schedule:
+            if e.adds_input:
+                ops.add_(h, h0)
             self.layers[e.layer].forward(h, ctx, cache.layer(e.cache), e.writes_cache)
         if ctx.n_logit_rows == 0:
             return None

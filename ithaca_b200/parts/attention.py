@@ -10,6 +10,16 @@ unless the spec gives one; softmax and the weighted sum are float32
 
 The three projections are stacked into one product, as the reference does for a
 fused ``attn_qkv`` tensor (src/model.cpp:1164-1170).
+
+Options a spec may give (all off by default):
+
+* ``v_head_dim``: value heads of another size than the key heads; the output projection then
+  takes n_heads * v_head_dim.
+* ``softcap``: scores become cap * tanh(score / cap) after the scale, before the mask.
+* ``conv_taps`` with the tensors ``q_conv``, ``k_conv``, ``v_conv`` [channels, taps]: a short causal
+  convolution over time on every channel of q, k and v, directly behind the projections and in
+  front of the rotation.  The last projected values of a sequence are part of its state: a ring
+  of ``taps`` positions per sequence beside its pages (``StateRequest``).
 """
 from __future__ import annotations
 
@@ -18,7 +28,7 @@ from typing import Dict, List, Mapping, Optional
 
 import torch
 
-from ..cache.cache import KVRequest, LayerCache
+from ..cache.cache import KVRequest, LayerCache, StateRequest
 from ..config.spec import PartSpec
 from ..csrc import ops
 from ..weights.loader import TensorReq
@@ -33,14 +43,26 @@ class Attention:
     def manifest(cls, spec: PartSpec) -> Dict[str, TensorReq]:
         d, nh, nkv, hd = spec["hidden_size"], spec["n_heads"], spec["n_kv_heads"], spec["head_dim"]
         w = spec.weights
-        return {w["q"]: TensorReq((nh * hd, d)), w["k"]: TensorReq((nkv * hd, d)),
-                w["v"]: TensorReq((nkv * hd, d)), w["o"]: TensorReq((d, nh * hd))}
+        hdv = spec.get("v_head_dim") or hd
+        out = {w["q"]: TensorReq((nh * hd, d)), w["k"]: TensorReq((nkv * hd, d)),
+               w["v"]: TensorReq((nkv * hdv, d)), w["o"]: TensorReq((d, nh * hdv))}
+        taps = spec.get("conv_taps") or 0
+        if taps:
+            # taps around 1/taps: the convolution keeps the projections' scale
+            for role, rows in (("q_conv", nh * hd), ("k_conv", nkv * hd), ("v_conv", nkv * hdv)):
+                out[w[role]] = TensorReq((rows, taps), std=1.0 / taps)
+        return out
 
     def __init__(self, spec: PartSpec, tensors: Mapping[str, torch.Tensor], runtime: Runtime, position=None):
         self.hidden = int(spec["hidden_size"])
         self.n_heads = int(spec["n_heads"])
         self.n_kv_heads = int(spec["n_kv_heads"])
         self.head_dim = int(spec["head_dim"])
+        self.v_head_dim = int(spec.get("v_head_dim") or self.head_dim)
+        self.softcap = float(spec.get("softcap") or 0.0)
+        self.conv_taps = int(spec.get("conv_taps") or 0)
+        if self.softcap < 0 or self.conv_taps < 0:
+            raise ValueError("attention: softcap and conv_taps cannot be negative")
         if self.n_heads % self.n_kv_heads:
             raise ValueError(f"attention: {self.n_heads} heads cannot share {self.n_kv_heads} kv heads evenly")
         self.window = spec.get("window")
@@ -59,7 +81,7 @@ class Attention:
         # and write q and the cache entries itself, without the [tokens, q+k+v] intermediate.
         self.pairing = position.pairing if position is not None else 0
         self.fused_rope = (runtime.dtype == "bfloat16" and position is not None and position.rotary_dim == self.head_dim
-                           and self.head_dim % 2 == 0)
+                           and self.head_dim % 2 == 0 and not self.conv_taps and self.v_head_dim == self.head_dim)
         if self.fused_rope and self.pairing == 0:
             half = self.head_dim // 2
             order = torch.stack((torch.arange(half), torch.arange(half) + half), dim=1).reshape(-1)
@@ -69,12 +91,24 @@ class Attention:
         self.qkv = Linear([wq, wk, tensors[w["v"]]], runtime)
         self.o = Linear([tensors[w["o"]]], runtime)
         self.runtime = runtime
+        self.conv_weight = None
+        self.channels = (self.n_heads + self.n_kv_heads) * self.head_dim + self.n_kv_heads * self.v_head_dim
+        if self.conv_taps:
+            cw = torch.cat([tensors[w[r]].to(torch.float32) for r in ("q_conv", "k_conv", "v_conv")], dim=0)
+            self.conv_weight = cw.to(runtime.device).contiguous()
+        # the plain path (projections, then convolution, rotation and append in one kernel) serves every option
+        self.plain_append = bool(self.conv_taps) or self.v_head_dim != self.head_dim
 
     def cache_requests(self) -> List[object]:
-        return [KVRequest(self.n_kv_heads, self.head_dim, self.window)]
+        v = self.v_head_dim if self.v_head_dim != self.head_dim else None
+        out: List[object] = [KVRequest(self.n_kv_heads, self.head_dim, self.window, v)]
+        if self.conv_taps > 1:
+            out.append(StateRequest("conv_ring", (self.conv_taps, self.channels), "float32"))
+        return out
 
     def forward(self, x: torch.Tensor, ctx, cache: LayerCache, residual: torch.Tensor,
-                writes_cache: bool = True) -> None:
+                writes_cache: bool = True, accumulate: bool = True) -> None:
+        """``accumulate=False``: the output replaces what ``residual`` holds instead of adding to it."""
         rt = self.runtime
         T = x.shape[0]
         q = torch.empty((T, self.n_heads * self.head_dim), dtype=rt.act_dtype, device=x.device)
@@ -89,26 +123,34 @@ class Attention:
             done = ops.gemm_qkv_rope(x, self.qkv.weight, q, cache.k_pages, cache.v_pages, cos_sin, ctx.token_seq,
                                      ctx.token_pos, table, self.n_heads, self.n_kv_heads, self.head_dim, writes_cache,
                                      rt.status)
-        if not done:
+        if self.plain_append:
+            qkv = self.qkv(x, out_dtype=torch.float32)
+            ring = cache.state("conv_ring") if self.conv_taps > 1 else None
+            ops.conv_rope_append(qkv, self.conv_weight, ring, ctx.slots, ctx.cu_seqlens, ctx.kv_lens, q, cache.k_pages,
+                                 cache.v_pages, ctx.token_seq, ctx.token_pos, table,
+                                 pos.inv_freq if pos is not None else None, self.n_heads, self.n_kv_heads,
+                                 pos.rotary_dim if pos is not None else 0, self.pairing, writes_cache, rt.status)
+        elif not done:
             qkv = self.qkv(x, out_dtype=torch.float32)
             ops.rope_append(qkv, q, cache.k_pages, cache.v_pages, ctx.token_seq, ctx.token_pos, table,
                             pos.inv_freq if pos is not None else None, self.n_heads, self.n_kv_heads, self.head_dim,
                             pos.rotary_dim if pos is not None else 0, self.pairing, writes_cache, rt.status)
-        att = attend(q, cache, ctx, table, self.n_heads, self.scale, self.window or 0, rt)
-        self.o(att, out=residual, accumulate=True)
+        att = attend(q, cache, ctx, table, self.n_heads, self.scale, self.window or 0, rt, self.softcap)
+        self.o(att, out=residual, accumulate=accumulate)
 
 
 def attend(q: torch.Tensor, cache: LayerCache, ctx, table: torch.Tensor, n_heads: int, scale: float, window: int,
-           rt: Runtime) -> torch.Tensor:
+           rt: Runtime, softcap: float = 0.0) -> torch.Tensor:
     """Chooses the attention kernel: tensor-core kernels for bfloat16 when they take the
-    head size, else the CUDA-core kernel (always for float32)."""
-    if q.dtype == torch.bfloat16:
+    head sizes, else the CUDA-core kernel (always for float32)."""
+    if q.dtype == torch.bfloat16 and cache.v_pages.shape[3] == cache.k_pages.shape[3]:
         from ..csrc import attention_bf16
-        out = attention_bf16.attend(q, cache.k_pages, cache.v_pages, ctx, table, n_heads, scale, window, rt.status)
+        out = attention_bf16.attend(q, cache.k_pages, cache.v_pages, ctx, table, n_heads, scale, window, rt.status,
+                                    softcap=softcap)
         if out is not None:
             return out
     return ops.attention_simt(q, cache.k_pages, cache.v_pages, ctx.token_seq, ctx.token_pos, table, n_heads, scale,
-                              window, rt.status)
+                              window, rt.status, softcap=softcap)
 
 
 register_mixer("attention", Attention)

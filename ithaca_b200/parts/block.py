@@ -3,6 +3,11 @@
 ``prenorm``: x += mixer(norm(x)); x += feed_forward(norm(x)) -- the order of the
 reference's layer loop (src/model.cpp:1460-1565).  The residual stream is float32
 and the parts add into it, so the sum never passes through 16 bits.
+
+``sandwich``: a norm in front of and behind each sublayer, and a constant on what joins the
+stream: x += m * norm_out(mixer(norm(x))); x += m * norm_out'(feed_forward(norm'(x))).  The
+sublayer writes into a float32 buffer of its own (the stream is not what it adds to); the norm
+behind it scales and adds in one kernel.  The feed-forward may be absent.
 """
 from __future__ import annotations
 
@@ -60,4 +65,60 @@ class PreNormBlock:
         self.feed_forward.forward(self.ff_norm.forward(residual), ctx, residual)
 
 
+class SandwichBlock:
+    NORMS = ("mixer", "mixer_out", "feed_forward", "feed_forward_out")
+
+    @classmethod
+    def manifest(cls, spec: BlockSpec) -> Dict[str, TensorReq]:
+        out: Dict[str, TensorReq] = {}
+        _merge(out, MIXERS.get(spec.mixer.kind).manifest(spec.mixer))
+        if spec.feed_forward is not None:
+            _merge(out, FEED_FORWARDS.get(spec.feed_forward.kind).manifest(spec.feed_forward))
+        for name, n in spec.norms.items():
+            if spec.feed_forward is None and name.startswith("feed_forward"):
+                continue
+            _merge(out, NORMS.get(n.kind).manifest(n))
+        if spec.position is not None:
+            _merge(out, POSITIONS.get(spec.position.kind).manifest(spec.position))
+        return out
+
+    def __init__(self, spec: BlockSpec, tensors: Mapping[str, torch.Tensor], runtime: Runtime):
+        has_ff = spec.feed_forward is not None
+        for need in self.NORMS[:2] + (self.NORMS[2:] if has_ff else ()):
+            if need not in spec.norms:
+                raise ValueError(f"sandwich block: the spec has no '{need}' norm")
+        self.mult = float(spec.params.get("residual_mult", 1.0))
+        position = None
+        if spec.position is not None:
+            position = POSITIONS.get(spec.position.kind)(spec.position, tensors, runtime)
+        mixer_cls = MIXERS.get(spec.mixer.kind)
+        if "position" in inspect.signature(mixer_cls.__init__).parameters:
+            self.mixer = mixer_cls(spec.mixer, tensors, runtime, position=position)
+        else:
+            self.mixer = mixer_cls(spec.mixer, tensors, runtime)
+        self.feed_forward = FEED_FORWARDS.get(spec.feed_forward.kind)(spec.feed_forward, tensors, runtime) if has_ff else None
+
+        def norm(name):
+            n = spec.norms[name]
+            made = NORMS.get(n.kind)(n, tensors, runtime)
+            if name.endswith("_out") and not hasattr(made, "add_into"):
+                raise ValueError(f"sandwich block: norm kind '{n.kind}' cannot stand behind a sublayer")
+            return made
+
+        self.mixer_norm, self.mixer_out_norm = norm("mixer"), norm("mixer_out")
+        self.ff_norm, self.ff_out_norm = (norm("feed_forward"), norm("feed_forward_out")) if has_ff else (None, None)
+
+    def cache_requests(self) -> List[object]:
+        return list(self.mixer.cache_requests())
+
+    def forward(self, residual: torch.Tensor, ctx, cache: LayerCache, writes_cache: bool = True) -> None:
+        y = torch.empty_like(residual)
+        self.mixer.forward(self.mixer_norm.forward(residual), ctx, cache, y, writes_cache, accumulate=False)
+        self.mixer_out_norm.add_into(y, residual, self.mult)
+        if self.feed_forward is not None:
+            self.feed_forward.forward(self.ff_norm.forward(residual), ctx, y, accumulate=False)
+            self.ff_out_norm.add_into(y, residual, self.mult)
+
+
 register_block("prenorm", PreNormBlock)
+register_block("sandwich", SandwichBlock)

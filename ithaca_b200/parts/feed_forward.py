@@ -42,14 +42,14 @@ class GatedMLP:
             wgu = self.gate_up.weight
             self.gate_up.weight = torch.stack((wgu[:ff], wgu[ff:]), dim=1).reshape(2 * ff, d).contiguous()
 
-    def forward(self, x: torch.Tensor, ctx, residual: torch.Tensor) -> None:
+    def forward(self, x: torch.Tensor, ctx, residual: torch.Tensor, accumulate: bool = True) -> None:
         if self.fused:
             from ..csrc import gemm_bf16
             h = gemm_bf16.gemm_swiglu(x, self.gate_up.weight, self.runtime.act_dtype)
         else:
             gu = self.gate_up(x, out_dtype=torch.float32)
             h = ops.swiglu(gu, self.runtime.act_dtype)
-        self.down(h, out=residual, accumulate=True)
+        self.down(h, out=residual, accumulate=accumulate)
 
 
 register_feed_forward("gated_mlp", GatedMLP)

@@ -1,5 +1,9 @@
 """RMS norm: y = x * (1 / sqrt(mean(x^2) + eps)) * w, in float32
-(src/model.cpp:626-633; GPU kernel src/gpu_kernels.cpp:1177-1195)."""
+(src/model.cpp:626-633; GPU kernel src/gpu_kernels.cpp:1177-1195).
+
+Layer norm: y = (x - mean) / sqrt(var + eps) * w + b with var the mean of the squared
+deviations, in float32.  A norm may also stand behind a sublayer: ``add_into`` then adds
+``mult * y`` to the residual stream in the same kernel."""
 from __future__ import annotations
 
 from typing import Dict, Mapping, Optional
@@ -28,4 +32,27 @@ class RMSNorm:
         return ops.rmsnorm(x, self.weight, self.eps, out_dtype or self.runtime.act_dtype, rows_in=rows)
 
 
+class LayerNorm:
+    @classmethod
+    def manifest(cls, spec: PartSpec) -> Dict[str, TensorReq]:
+        return {spec.weights["weight"]: TensorReq((spec["size"],), init="ones"),
+                spec.weights["bias"]: TensorReq((spec["size"],))}
+
+    def __init__(self, spec: PartSpec, tensors: Mapping[str, torch.Tensor], runtime: Runtime):
+        self.size = int(spec["size"])
+        self.eps = float(spec["eps"])
+        self.weight = as_float32(tensors[spec.weights["weight"]], runtime)
+        self.bias = as_float32(tensors[spec.weights["bias"]], runtime)
+        self.runtime = runtime
+
+    def forward(self, x: torch.Tensor, rows: Optional[torch.Tensor] = None,
+                out_dtype: Optional[torch.dtype] = None) -> torch.Tensor:
+        return ops.layernorm(x, self.weight, self.bias, self.eps, out_dtype or self.runtime.act_dtype, rows_in=rows)
+
+    def add_into(self, x: torch.Tensor, residual: torch.Tensor, mult: float = 1.0) -> None:
+        """residual += mult * norm(x)"""
+        ops.layernorm(x, self.weight, self.bias, self.eps, torch.float32, into=residual, mult=mult)
+
+
 register_norm("rmsnorm", RMSNorm)
+register_norm("layernorm", LayerNorm)
