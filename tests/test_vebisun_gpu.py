@@ -1,0 +1,367 @@
+"""The Vebisun decoder and its mechanisms against the plain implementation (tests/plain/vebisun_plain.py).
+
+Small configurations with random weights, made here.  Per mechanism: the kernel against the plain
+function.  Whole models: prompts against token-by-token decoding, portions down to two tokens, batches of
+unequal requests against each alone, slots and pages that are used again, keys at page and window edges in
+prompts and in decoding, long decoding, and greedy generation through the engine's own loop.  Where random
+weights would hide a fault (a window one key off, a far key), the weights are made so that one key decides
+the result.
+"""
+import copy
+import json
+import os
+
+import numpy as np
+import pytest
+import torch
+
+from helpers import REL, random_ids, rel_err, run_schedule
+from plain import vebisun_plain as P
+
+pytestmark = pytest.mark.gpu
+
+ROT = {"base": 1000.0, "dims": 8, "scaling": {"factor": 4.0, "high": 4.0, "low": 1.0, "original": 24}}
+
+
+def _moe(E, top, ff, groups=None):
+    r = {"experts": E, "top": top}
+    if groups:
+        r["groups"] = {"count": groups[0], "keep": groups[1]}
+    return {"kind": "moe", "expert": {"ff": ff}, "router": r}
+
+
+def _mixer(heads, kv, dim, vdim, conv=None, rot=None, window=None, softcap=None, scale=8.0):
+    m = {"heads": heads, "kv_heads": kv, "dim": dim, "vdim": vdim, "scale": scale}
+    if conv is not None:
+        m["conv"] = conv
+    if rot is not None:
+        m["rot"] = rot
+    if window is not None:
+        m["mask"] = {"size": window}
+    if softcap is not None:
+        m["softcap"] = softcap
+    return m
+
+
+# three unlike layers, a loop over the last two that runs three times
+CFG_A = {
+    "architecture": "Vebisun", "vocab": 97, "width": 64, "embedding": {"scale": 2.5}, "residual_mult": 0.7,
+    "norm": {"eps": 1e-5},
+    "layers": [
+        {"type": "attention", "mixer": _mixer(4, 2, 16, 24, conv=3, rot=ROT, window=9, softcap=3.0),
+         "mlp": _moe(8, 3, 40, groups=(4, 2))},
+        {"type": "attention", "mixer": _mixer(2, 2, 32, 32, conv=2, rot={"base": 50.0, "dims": 32}), "mlp": None},
+        {"type": "attention", "mixer": _mixer(3, 1, 16, 16, window=70, softcap=5.0), "mlp": _moe(4, 1, 24)},
+    ],
+    "loop": {"start": 1, "stop": 3, "times": 3},
+}
+# no loop; a window of exactly one page and of one key; four taps and one tap; every expert used; one group kept of one
+CFG_B = {
+    "architecture": "Vebisun", "vocab": 61, "width": 48, "embedding": {"scale": 1.0}, "residual_mult": 1.0,
+    "norm": {"eps": 1e-6},
+    "layers": [
+        {"type": "attention", "mixer": _mixer(3, 3, 16, 8, conv=4, rot={"base": 10000.0, "dims": 16}, window=64, softcap=2.0),
+         "mlp": _moe(3, 3, 20, groups=(1, 1))},
+        {"type": "attention", "mixer": _mixer(1, 1, 32, 48, conv=1, rot=ROT, window=1), "mlp": _moe(6, 2, 16, groups=(3, 3))},
+    ],
+}
+CONFIGS = {"A": CFG_A, "B": CFG_B}
+
+
+def _write(tmp, cfg, seed, tensors=None):
+    from ithaca_b200.weights import write_random_model
+    d = os.path.join(str(tmp), f"m{abs(hash(json.dumps(cfg, sort_keys=True))) % 10**8}_{seed}")
+    write_random_model(d, cfg, seed)
+    if tensors is not None:
+        from ithaca_b200.weights.safetensors_io import write_file
+        write_file(os.path.join(d, "model.safetensors"), tensors, {"format": "pt"})
+    return d
+
+
+def _load(d):
+    from safetensors import safe_open
+    t = {}
+    with safe_open(os.path.join(d, "model.safetensors"), framework="pt") as f:
+        for k in f.keys():
+            t[k] = f.get_tensor(k)
+    with open(os.path.join(d, "config.json")) as f:
+        return json.load(f), t
+
+
+@pytest.fixture(scope="module")
+def models(tmp_path_factory):
+    root = tmp_path_factory.mktemp("vebisun")
+    return {n: _write(root, c, seed=5 + i) for i, (n, c) in enumerate(CONFIGS.items())}
+
+
+def _close(got, want, dtype):
+    """float32: every logit within the tolerance.  bfloat16: a router reads the 16-bit rounding of its input, so among
+    hundreds of random tokens a few sit close enough to a tie to choose another expert than the float64 side; such
+    a token's row is off by more than rounding.  Nine rows in ten must hold the tolerance and none may be far off
+    (a wrong key or a lost state moves a row by tens of percent, see the one-key test, which has no router)."""
+    got, want = np.asarray(got, dtype=np.float64), np.asarray(want, dtype=np.float64)
+    assert got.shape == want.shape and np.all(np.isfinite(got))
+    rows = np.abs(got - want).reshape(-1, want.shape[-1]).max(-1) / max(np.abs(want).max(), 1e-30)
+    if dtype == "float32":
+        return bool(rows.max() < REL[dtype])
+    return bool(np.mean(rows < REL[dtype]) >= 0.9 and rows.max() < 5 * REL[dtype])
+
+
+def _plain(d, ids):
+    cfg, t = _load(d)
+    return P.forward(ids, cfg, t).numpy()
+
+
+# ------------------------------------------------------------------------------------------ configuration
+def test_config_reads_every_size_from_the_file(models):
+    from ithaca_b200.config import config_from_model_dir, validate_schedule
+    arch, cfg = config_from_model_dir(models["A"])
+    spec = cfg.model_spec()
+    validate_schedule(spec)
+    assert arch.name == "Vebisun" and spec.vocab_size == 97 and spec.hidden_size == 64
+    runs = [(e.layer, e.adds_input) for e in spec.schedule]
+    assert runs == [(0, False), (1, False), (2, False), (1, True), (2, False), (1, True), (2, False)]
+    assert len({e.cache for e in spec.schedule}) == len(spec.schedule)            # every pass has its own cache
+    assert runs == P.layer_runs(CFG_A)
+    assert spec.layers[1].feed_forward is None and spec.layers[0].mixer["v_head_dim"] == 24
+
+
+# ------------------------------------------------------------------------------------------ mechanisms alone
+@pytest.mark.parametrize("d", [48, 256, 5000])
+def test_layer_norm_kernel(d):
+    from ithaca_b200.csrc import ops
+    g = torch.Generator().manual_seed(d)
+    x = (torch.randn(7, d, generator=g) * 3 + 1.5).cuda()
+    w, b = torch.randn(d, generator=g).cuda(), torch.randn(d, generator=g).cuda()
+    want = P.layer_norm(x.double().cpu(), w.cpu(), b.cpu(), 1e-5)
+    got = ops.layernorm(x, w, b, 1e-5, torch.float32)
+    assert rel_err(got.cpu().numpy(), want.numpy()) < 2e-6
+    rows = torch.tensor([5, 0, 5], dtype=torch.int32).cuda()
+    assert torch.equal(ops.layernorm(x, w, b, 1e-5, torch.float32, rows_in=rows), got[rows.long()])
+    assert rel_err(ops.layernorm(x, w, b, 1e-5, torch.bfloat16).float().cpu().numpy(), want.numpy()) < 1e-2
+    stream = torch.randn(7, d, generator=g).cuda()
+    want2 = stream.double().cpu() + 0.3 * want
+    ops.layernorm(x, w, b, 1e-5, torch.float32, into=stream, mult=0.3)
+    assert rel_err(stream.cpu().numpy(), want2.numpy()) < 2e-6
+
+
+@pytest.mark.parametrize("E,top,groups", [(8, 3, (4, 2)), (16, 2, (2, 1)), (6, 6, None), (5, 1, None), (12, 4, (3, 3)), (64, 8, (8, 3))])
+def test_router_kernel(E, top, groups):
+    from ithaca_b200.csrc import ops
+    g = torch.Generator().manual_seed(E * 10 + top)
+    z = torch.randn(50, E, generator=g) * 2
+    rc = {"experts": E, "top": top}
+    if groups:
+        rc["groups"] = {"count": groups[0], "keep": groups[1]}
+    want_e, want_w = P.route(z.double(), rc, torch.eye(E))
+    got_e, got_w = ops.moe_route(z.cuda(), top, *(groups or (0, 0)))
+    assert torch.equal(got_e.cpu().long(), want_e)
+    assert rel_err(got_w.cpu().numpy(), want_w.numpy()) < 1e-6
+
+
+def test_router_prefers_the_better_group_over_the_better_expert():
+    """Two groups of two; the best single expert sits in group 0, but only one group is kept and two experts are
+    chosen: both come from the group whose best is best, whatever the other group's second holds."""
+    from ithaca_b200.csrc import ops
+    z = torch.tensor([[3.0, -5.0, 2.5, 2.4], [0.0, 1.0, 5.0, -9.0]]).cuda()
+    e, w = ops.moe_route(z, 2, 2, 1)
+    assert e.cpu().tolist() == [[0, 1], [2, 3]]
+    s = torch.softmax(z.cpu(), -1)
+    assert torch.allclose(w.cpu(), torch.stack([s[0, [0, 1]], s[1, [2, 3]]]), atol=1e-7)          # not renormalized
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("T,E,top,ff,d", [(1, 4, 2, 24, 32), (70, 8, 3, 40, 64), (300, 3, 1, 100, 72)])
+def test_mixture_of_experts_part(dtype, T, E, top, ff, d):
+    from ithaca_b200.config.spec import PartSpec
+    from ithaca_b200.parts import FEED_FORWARDS, Runtime
+    g = torch.Generator().manual_seed(T)
+    spec = PartSpec("moe", {"hidden_size": d, "intermediate_size": ff, "n_experts": E, "top": top},
+                    {"router": "router", "gate": "e{e}.gate", "up": "e{e}.up", "down": "e{e}.down"})
+    t = {"router": (torch.randn(E, d, generator=g) * 0.4).bfloat16()}
+    for e in range(E):
+        t[f"e{e}.gate"] = (torch.randn(ff, d, generator=g) * 0.3).bfloat16()
+        t[f"e{e}.up"] = (torch.randn(ff, d, generator=g) * 0.3).bfloat16()
+        t[f"e{e}.down"] = (torch.randn(d, ff, generator=g) * 0.3).bfloat16()
+    rt = Runtime(dtype=dtype, device="cuda:0")
+    part = FEED_FORWARDS.get("moe")(spec, t, rt)
+    x = torch.randn(T, d, generator=g).bfloat16()
+    want = P.moe_ff(x.double(), {"router": {"experts": E, "top": top}}, t, "")
+    out = torch.full((T, d), 7.0, device="cuda")
+    part.forward(x.cuda().to(rt.act_dtype), None, out, accumulate=False)
+    assert rel_err(out.cpu().numpy(), want.numpy()) < (2e-5 if dtype == "float32" else 2e-2)
+    base = torch.ones(T, d, device="cuda")
+    part.forward(x.cuda().to(rt.act_dtype), None, base, accumulate=True)
+    assert torch.allclose(base - 1.0, out, atol=1e-5 * float(out.abs().max()))
+
+
+# ------------------------------------------------------------------------------------------ whole models
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("name", ["A", "B"])
+def test_whole_prompt_matches_plain(models, name, dtype):
+    from ithaca_b200 import Engine
+    ids = random_ids(150, CONFIGS[name]["vocab"], 3)
+    want = _plain(models[name], ids)
+    eng = Engine(models[name], dtype=dtype, max_tokens=1024)
+    s = eng.alloc_slot()
+    got = eng.step([s], [ids], "all").cpu().numpy()
+    eng.check_status()
+    assert _close(got, want, dtype)
+    # the first tokens of a sequence alone
+    for n in (1, 2, 3):
+        s2 = eng.alloc_slot()
+        assert _close(eng.step([s2], [ids[:n]], "all").cpu().numpy(), want[:n], dtype)
+        eng.free_slot(s2)
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("name", ["A", "B"])
+def test_schedules_agree_with_plain(models, name, dtype):
+    """Token by token; portions of 2, 3, 7, 64 and 65 tokens; a prompt and then decoding across page and window
+    edges; unequal requests in one batch and decoded together; every position against the plain whole sequence."""
+    from ithaca_b200 import Engine
+    V = CONFIGS[name]["vocab"]
+    reqs = {"a": random_ids(140, V, 11), "b": random_ids(67, V, 12), "c": random_ids(1, V, 13), "d": random_ids(9, V, 14)}
+    want = {r: _plain(models[name], ids) for r, ids in reqs.items()}
+    eng = Engine(models[name], dtype=dtype, max_tokens=2048)
+
+    def portions(r, sizes):
+        out, left = [], len(reqs[r])
+        while left:
+            for n in sizes:
+                n = min(n, left)
+                if n:
+                    out.append([(r, n)])
+                    left -= n
+        return out
+
+    schedules = {
+        "token by token": [[("b", 1)] for _ in range(67)],
+        "portions": portions("a", [2, 3, 7, 64, 65]),
+        "pairs": portions("b", [2]),
+        "prompt then decode": [[("a", 60)]] + [[("a", 1)] for _ in range(80)],
+        "batch": [[("c", 1), ("a", 100), ("d", 5), ("b", 30)]] + [[("a", 1), ("d", 1), ("b", 1)] for _ in range(4)]
+                 + [[("a", 1), ("b", 1)] for _ in range(33)] + [[("a", 1)] for _ in range(3)],
+        "mixed portions": [[("a", 64), ("b", 1)], [("b", 64), ("a", 3)], [("a", 73), ("b", 2)]],
+    }
+    for label, sched in schedules.items():
+        got = run_schedule(eng, reqs, sched)
+        for r, lg in got.items():
+            assert _close(lg, want[r], dtype), (label, r)
+        eng.cache.table.check_consistent()
+        assert eng.cache.table.n_slots_in_use() == 0
+
+
+def test_slots_and_pages_are_used_again(models):
+    """A small cache: requests come and go, so slots, pages and convolution rings are handed out again, also to
+    shorter sequences whose first tokens must see nothing of what lay there before."""
+    from ithaca_b200 import Engine
+    V = CFG_A["vocab"]
+    eng = Engine(models["A"], dtype="float32", max_tokens=64 * 6, max_slots=2)
+    for round_ in range(4):
+        reqs = {"x": random_ids(130 - 40 * round_, V, 20 + round_), "y": random_ids(3 + round_, V, 30 + round_)}
+        got = run_schedule(eng, reqs, [[("x", len(reqs["x"]) - 2), ("y", 2)], [("x", 1), ("y", 1)], [("x", 1)]]
+                           + [[("y", 1)] for _ in range(round_)])
+        for r, ids in reqs.items():
+            assert rel_err(got[r], _plain(models["A"], ids)) < REL["float32"], (round_, r)
+        eng.cache.table.check_consistent()
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_long_decoding(models, dtype):
+    from ithaca_b200 import Engine
+    ids = random_ids(330, CFG_A["vocab"], 77)
+    want = _plain(models["A"], ids)
+    eng = Engine(models["A"], dtype=dtype, max_tokens=1024)
+    got = run_schedule(eng, {"a": ids}, [[("a", 10)]] + [[("a", 1)] for _ in range(320)])["a"]
+    assert _close(got, want, dtype)
+
+
+# ------------------------------------------------------------------------------------------ one key decides
+def _needle_model(tmp, window, conv):
+    """One layer whose attention output is, to good approximation, the value of the one earlier 'needle' token
+    that the query token matches: needle and query point along axis 0, every other token along an axis of its own,
+    and q and k copy axis 0 of the normed input.  If a window or a page edge is one key off, the logits at the query
+    change completely."""
+    from ithaca_b200.config import config_from_dict
+    from ithaca_b200.engine.model import weight_manifest
+    from ithaca_b200.weights.random_init import random_tensors
+    d = 32
+    cfg = {"architecture": "Vebisun", "vocab": 40, "width": d, "embedding": {"scale": 1.0}, "residual_mult": 1.0,
+           "norm": {"eps": 1e-6},
+           "layers": [{"type": "attention", "mixer": _mixer(1, 1, d, d, conv=conv, window=window, scale=0.05), "mlp": None}]}
+    t = random_tensors(weight_manifest(config_from_dict(cfg)[1].model_spec()), 3, "bfloat16")
+    g = torch.Generator().manual_seed(1)
+    emb = torch.randn(40, d, generator=g) * 0.05
+    for i in range(3, 40):
+        emb[i, 8 + i % 20] += 4.0
+    emb[1] += torch.eye(d)[0] * 4 + torch.eye(d)[5] * 2          # the needle's token
+    emb[2] += torch.eye(d)[0] * 4 - torch.eye(d)[5] * 2          # the query's token: matches the needle along axis 0
+    t["embed"] = emb.bfloat16()
+    t["l0.norm1"], t["l0.norm1.b"] = torch.ones(d).bfloat16(), torch.zeros(d).bfloat16()
+    t["l0.mix.q"] = t["l0.mix.k"] = (torch.eye(d)[0][None, :] * torch.eye(d)[0][:, None] * 4).bfloat16()
+    t["l0.mix.v"] = torch.eye(d).bfloat16()
+    if conv:
+        for r in "qkv":                                            # the tap at the token itself is 1, the others small
+            w = torch.full((d, conv), 0.05)
+            w[:, -1] = 1.0
+            t[f"l0.mix.{r}.conv"] = w.bfloat16()
+    return _write(tmp, cfg, 3, tensors=t), cfg
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("window,conv", [(72, 3), (64, None), (None, 2), (130, None)])
+def test_the_one_key_that_matters(tmp_path, window, conv, dtype):
+    """The needle sits far back, at a page's last and first place, and just inside and just outside the window; the
+    query comes at the end of a prompt or is decoded alone after it."""
+    from ithaca_b200 import Engine
+    d, cfg = _needle_model(tmp_path, window, conv)
+    eng = Engine(d, dtype=dtype, max_tokens=4096)
+    n = 400
+    places = [0, 63, 64, 127, 128, n - 2]
+    if window:
+        places += [n - 1 - window, n - window, n - window + 1, n - 1 - 64, n - 64]
+    hay = [3 + (i * 7) % 37 for i in range(n)]
+    seen = []
+    for at in sorted(set(p for p in places if 0 <= p < n - 1)):
+        ids = list(hay)
+        ids[at], ids[n - 1] = 1, 2
+        want = _plain(d, ids)[n - 1]
+        for cut in (n, n - 1, n - 5):                              # whole prompt; the query decoded alone; a short portion
+            s = eng.alloc_slot()
+            steps = [ids[:cut]] + [[x] for x in ids[cut:]]
+            for st in steps:
+                lg = eng.step([s], [st], "last")
+            eng.free_slot(s)
+            assert rel_err(lg.cpu().numpy()[0], want) < REL[dtype], (at, cut)
+        seen.append(float(np.abs(want).max()))
+    eng.check_status()
+    if window:                                                     # the test has teeth: inside and outside differ widely
+        ids_in, ids_out = list(hay), list(hay)
+        ids_in[n - window], ids_out[n - 1 - window] = 1, 1
+        ids_in[n - 1] = ids_out[n - 1] = 2
+        a, b = _plain(d, ids_in)[n - 1], _plain(d, ids_out)[n - 1]
+        assert rel_err(a, b) > 0.2
+
+
+# ------------------------------------------------------------------------------------------ generation
+@pytest.mark.parametrize("graphs", [True, False])
+@pytest.mark.parametrize("name", ["A", "B"])
+def test_greedy_generation_through_the_engine(models, name, graphs):
+    """More prompts than slots, unequal lengths, the generation loop's own batching (and its graph-replayed decode
+    steps, which launch a step ahead and may drop it)."""
+    from ithaca_b200 import Engine
+    V = CONFIGS[name]["vocab"]
+    cfg, t = _load(models[name])
+    prompts = [random_ids(n, V, 60 + n) for n in (1, 6, 70, 20)]
+    eng = Engine(models[name], dtype="float32", max_tokens=64 * 12, max_slots=3, graphs=graphs)
+    got = eng.generate(prompts, max_tokens=12, temp=0.0, rep_pen=1.0, stop_token_ids=[])
+    for p, g in zip(prompts, got):
+        assert len(g) == 12
+        lgs = P.forward(list(p) + g[:-1], cfg, t)                  # every generated token is the plain model's greedy pick
+        for i, tok in enumerate(g):
+            lg = lgs[len(p) - 1 + i]
+            top2 = torch.topk(lg, 2).values
+            if float(top2[0] - top2[1]) > 1e-4 * float(lg.abs().max()):
+                assert tok == int(lg.argmax()), (len(p), i)
+    assert eng.cache.table.n_slots_in_use() == 0
