@@ -60,6 +60,17 @@ __device__ __forceinline__ void mma(float (&c)[4], const uint32_t (&a)[4], uint3
         : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
         : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
 }
+// A score in base 2: s * a, or, with a cap on the scores, cap * tanh(s * scale / cap) * log2 e = b * tanh(s * a)
+// (a = scale / cap, b = cap * log2 e; b = 0 means no cap and a = scale * log2 e).  The hardware's tanh has a relative
+// error near 2^-11, below what the 16-bit queries and keys leave in a score.
+__device__ __forceinline__ float ik_tanh_fast(float x) {
+    float y;
+    asm("tanh.approx.f32 %0, %1;" : "=f"(y) : "f"(x));
+    return y;
+}
+__device__ __forceinline__ float ik_capped(float s, float a, float b) {
+    return b != 0.f ? b * ik_tanh_fast(s * a) : s * a;
+}
 __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
     __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
     return *reinterpret_cast<uint32_t*>(&v);
@@ -70,7 +81,7 @@ template <int NW>
 __global__ void __launch_bounds__(32 * NW)
 attn_prefill_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k_pages, const bf16* __restrict__ v_pages,
                     bf16* __restrict__ out, const int* __restrict__ cu_seqlens, const int* __restrict__ kv_lens,
-                    const int* __restrict__ table, int table_stride, int nh, int nkv, float scale_log2e, int window,
+                    const int* __restrict__ table, int table_stride, int nh, int nkv, float scale_log2e, float cap_log2e, int window,
                     int n_pages, int* status) {
     ik_pdl_wait();
     ik_pdl_launch_dependents();
@@ -161,7 +172,7 @@ attn_prefill_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k_pages
             for (int e = 0; e < 4; e++) {
                 const int r = e >> 1, j = jbase + n * 8 + (e & 1);
                 const bool ok = my_row[r] && j <= my_pos[r] && (window <= 0 || j > my_pos[r] - window);
-                const float v = ok ? s[n][e] * scale_log2e : -INFINITY;
+                const float v = ok ? ik_capped(s[n][e], scale_log2e, cap_log2e) : -INFINITY;
                 s[n][e] = v;
                 mx[r] = fmaxf(mx[r], v);
             }
@@ -256,7 +267,7 @@ __global__ void __launch_bounds__(192, 2)
 attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
                        const __grid_constant__ CUtensorMap map_v, bf16* __restrict__ out,
                        const int* __restrict__ cu_seqlens, const int* __restrict__ kv_lens,
-                       const int* __restrict__ table, int table_stride, int nh, int nkv, float scale_log2e,
+                       const int* __restrict__ table, int table_stride, int nh, int nkv, float scale_log2e, float cap_log2e,
                        int window, int n_pages, int* status) {
     extern __shared__ __align__(1024) unsigned char tc_smem[];
     ik_pdl_wait();
@@ -404,6 +415,11 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
             #pragma unroll
             for (int c0 = 0; c0 < PAGE; c0 += 16) tmem_ld16_issue(lane_base + (i & 1) * PAGE + c0, sc + c0);
             tmem_ld_wait();
+            if (cap_log2e != 0.f) {                        // capped scores: tanh is monotone, so the maximum below still holds
+                #pragma unroll
+                for (int c = 0; c < PAGE; c++) sc[c] = cap_log2e * ik_tanh_fast(sc[c] * scale_log2e);
+            }
+            const float mul = cap_log2e != 0.f ? 1.f : scale_log2e;
             const bool need_mask = (p * PAGE + PAGE - 1 > pos_lo) || (window > 0 && p * PAGE < pos_hi + 1 - window);
             // Few instructions per score: the maximum is taken over the raw scores and scaled once (the scale is
             // positive), and the scaling of a score is folded into the subtraction of the reference below.  Four
@@ -423,7 +439,7 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
                 #pragma unroll
                 for (int c = 0; c < PAGE; c += 2) mx4[(c >> 1) & 3] = max3(mx4[(c >> 1) & 3], sc[c], sc[c + 1]);
             }
-            const float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3])) * scale_log2e;
+            const float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3])) * mul;
             // m is the reference the exponentials are taken against.  It follows the running maximum only when
             // that has moved by more than 8 (a factor 256): until then the probabilities may exceed 1 by that
             // factor, which float sums and bfloat16 operands take in their stride, and O needs no rescaling.
@@ -437,7 +453,7 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
             #pragma unroll
             for (int c = 0; c < PAGE; c += 2) {            // two scores per multiply-add and per add
                 float a0, a1;
-                fma_f32x2(a0, a1, sc[c], sc[c + 1], scale_log2e, -m_use);
+                fma_f32x2(a0, a1, sc[c], sc[c + 1], mul, -m_use);
                 sc[c] = ik_ex2(a0);
                 sc[c + 1] = ik_ex2(a1);
                 add_f32x2(sum4[c & 2], sum4[(c & 2) + 1], sc[c], sc[c + 1]);
@@ -525,7 +541,7 @@ template <int NS>
 __global__ void __launch_bounds__(128)
 attn_decode_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k_pages, const bf16* __restrict__ v_pages,
                    float* __restrict__ part_o, float* __restrict__ part_ml, const int* __restrict__ kv_lens,
-                   const int* __restrict__ table, int table_stride, int nh, int nkv, float scale_log2e, int window,
+                   const int* __restrict__ table, int table_stride, int nh, int nkv, float scale_log2e, float cap_log2e, int window,
                    int n_pages, int chunk_pages, int n_splits, int* status) {
     ik_pdl_wait();
     constexpr int CH = HD / 8;
@@ -611,7 +627,7 @@ attn_decode_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k_pages,
             for (int e = 0; e < 4; e++) {
                 const int r = e >> 1, j = jbase + n * 8 + (e & 1);
                 const bool ok = my_row[r] && j <= pos && j >= j0;
-                const float v = ok ? s[n][e] * scale_log2e : -INFINITY;
+                const float v = ok ? ik_capped(s[n][e], scale_log2e, cap_log2e) : -INFINITY;
                 s[n][e] = v;
                 mx[r] = fmaxf(mx[r], v);
             }
@@ -733,8 +749,9 @@ IK_EXPORT int ik_attn_take_wait_record(int* out4) { return ik_take_wait_record(o
 
 IK_EXPORT int ik_attn_prefill(const void* q, const void* k_pages, const void* v_pages, void* out, const int* cu_seqlens,
                               const int* kv_lens, const int* table, int table_stride, int B, int max_new, int nh,
-                              int nkv, float scale, int window, int page_size, int n_pages, int* status,
+                              int nkv, float scale, float softcap, int window, int page_size, int n_pages, int* status,
                               cudaStream_t stream) {
+    const float sc_a = softcap > 0.f ? scale / softcap : scale * 1.4426950408889634f, sc_b = softcap > 0.f ? softcap * 1.4426950408889634f : 0.f;
     if (B <= 0 || max_new <= 0 || nh <= 0 || nkv <= 0 || nh % nkv || page_size != PAGE || B > 65535 || nh > 65535)
         return IK_BAD_ARGUMENT;
     constexpr int NW = 4, BM = 16 * NW;
@@ -747,16 +764,17 @@ IK_EXPORT int ik_attn_prefill(const void* q, const void* k_pages, const void* v_
     dim3 grid((max_new + BM - 1) / BM, nh, B);
     IK_RETURN_IF_ERROR(ik_launch(kern, grid, 32 * NW, smem, stream, (const bf16*)q, (const bf16*)k_pages, (const bf16*)v_pages, (bf16*)out,
                                           cu_seqlens, kv_lens, table, table_stride, nh, nkv,
-                                          scale * 1.4426950408889634f, window, n_pages, status));
+                                          sc_a, sc_b, window, n_pages, status));
     IK_LAUNCH_STATUS();
 }
 
 // The tcgen05 kernel (head sizes 64 and 128; IK_UNSUPPORTED otherwise).  T: rows of q.
 IK_EXPORT int ik_attn_prefill_tc(const void* q, const void* k_pages, const void* v_pages, void* out, const int* cu_seqlens,
                                  const int* kv_lens, const int* table, int table_stride, int T, int B, int max_new, int nh,
-                                 int nkv, float scale, int window, int page_size, int n_pages, int* status,
+                                 int nkv, float scale, float softcap, int window, int page_size, int n_pages, int* status,
                                  cudaStream_t stream) {
 #if IK_HD == 64 || IK_HD == 128
+    const float sc_a = softcap > 0.f ? scale / softcap : scale * 1.4426950408889634f, sc_b = softcap > 0.f ? softcap * 1.4426950408889634f : 0.f;
     if (T <= 0 || B <= 0 || max_new <= 0 || nh <= 0 || nkv <= 0 || nh % nkv || page_size != PAGE || B > 65535 || nh > 65535)
         return IK_BAD_ARGUMENT;
     if (((uintptr_t)q % 16) || ((uintptr_t)k_pages % 16) || ((uintptr_t)v_pages % 16)) return IK_UNSUPPORTED;
@@ -774,7 +792,7 @@ IK_EXPORT int ik_attn_prefill_tc(const void* q, const void* k_pages, const void*
     if (e != cudaSuccess) return (int)e;
     dim3 grid((max_new + TC_BM - 1) / TC_BM, nh, B);
     IK_RETURN_IF_ERROR(ik_launch(kern, grid, 192, TC_SMEM, stream, mq, mk, mv, (bf16*)out, cu_seqlens, kv_lens, table,
-                                 table_stride, nh, nkv, scale * 1.4426950408889634f, window, n_pages, status));
+                                 table_stride, nh, nkv, sc_a, sc_b, window, n_pages, status));
     IK_LAUNCH_STATUS();
 #else
     return IK_UNSUPPORTED;
@@ -785,8 +803,9 @@ IK_EXPORT int ik_attn_prefill_tc(const void* q, const void* k_pages, const void*
 // n_splits must cover the longest sequence: n_splits * chunk_pages * 64 >= max kv length.
 IK_EXPORT int ik_attn_decode(const void* q, const void* k_pages, const void* v_pages, void* out, float* part_o,
                              float* part_ml, const int* kv_lens, const int* table, int table_stride, int B, int nh,
-                             int nkv, float scale, int window, int page_size, int n_pages, int chunk_pages,
+                             int nkv, float scale, float softcap, int window, int page_size, int n_pages, int chunk_pages,
                              int n_splits, int ring_kb, int* status, cudaStream_t stream) {
+    const float sc_a = softcap > 0.f ? scale / softcap : scale * 1.4426950408889634f, sc_b = softcap > 0.f ? softcap * 1.4426950408889634f : 0.f;
     if (B <= 0 || nh <= 0 || nkv <= 0 || nh % nkv || page_size != PAGE || chunk_pages <= 0 || n_splits <= 0 ||
         n_splits > 65535)
         return IK_BAD_ARGUMENT;
@@ -807,7 +826,7 @@ IK_EXPORT int ik_attn_decode(const void* q, const void* k_pages, const void* v_p
             if (e0 != cudaSuccess) return (int)e0;                                                                   \
         }                                                                                                            \
         IK_RETURN_IF_ERROR(ik_launch(kern, grid, 128, smem, stream, (const bf16*)q, (const bf16*)k_pages, (const bf16*)v_pages, part_o, part_ml, \
-                                          kv_lens, table, table_stride, nh, nkv, scale * 1.4426950408889634f, window, \
+                                          kv_lens, table, table_stride, nh, nkv, sc_a, sc_b, window, \
                                           n_pages, chunk_pages, n_splits, status));                                   \
     }
     if (ns == 2) IK_DEC(2) else if (ns == 3) IK_DEC(3) else IK_DEC(4)

@@ -79,6 +79,27 @@ def rotate_pairs(x: torch.Tensor, positions: Sequence[int], freqs: torch.Tensor)
     return out
 
 
+def attention_core(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, scale: float, cap=None, window=None) -> torch.Tensor:
+    """q [T, H, D], k [T, G, D], v [T, G, Dv] of one sequence -> [T, H, Dv]: scores * scale, capped by
+    cap * tanh(. / cap), position i sees j with 0 <= i - j < window, softmax, weighted values."""
+    T, H, _ = q.shape
+    G = k.shape[1]
+    out = torch.zeros(T, H, v.shape[2], dtype=q.dtype)
+    i = torch.arange(T)[:, None]
+    j = torch.arange(T)[None, :]
+    seen = j <= i
+    if window:
+        seen = seen & (i - j < window)
+    for hh in range(H):
+        g = hh // (H // G)
+        s = (q[:, hh] @ k[:, g].T) * float(scale)
+        if cap:
+            s = cap * torch.tanh(s / cap)
+        s = s.masked_fill(~seen, float("-inf"))
+        out[:, hh] = torch.softmax(s, dim=-1) @ v[:, g]
+    return out
+
+
 def attention_mixer(h: torch.Tensor, mc: Mapping, w: Mapping[str, torch.Tensor], prefix: str) -> torch.Tensor:
     T = h.shape[0]
     dt = h.dtype
@@ -95,21 +116,7 @@ def attention_mixer(h: torch.Tensor, mc: Mapping, w: Mapping[str, torch.Tensor],
     if rot:
         f = rotary_frequencies(rot["dims"], rot["base"], rot.get("scaling"))
         q, k = rotate_pairs(q, range(T), f), rotate_pairs(k, range(T), f)
-    out = torch.zeros(T, H, Dv, dtype=dt)
-    cap = mc.get("softcap")
-    window = (mc.get("mask") or {}).get("size")
-    for hh in range(H):
-        g = hh // (H // G)
-        s = (q[:, hh] @ k[:, g].T) * float(mc["scale"])
-        if cap:
-            s = cap * torch.tanh(s / cap)
-        i = torch.arange(T)[:, None]
-        j = torch.arange(T)[None, :]
-        seen = (j <= i)
-        if window:
-            seen = seen & (i - j < window)
-        s = s.masked_fill(~seen, float("-inf"))
-        out[:, hh] = torch.softmax(s, dim=-1) @ v[:, g]
+    out = attention_core(q, k, v, mc["scale"], mc.get("softcap"), (mc.get("mask") or {}).get("size"))
     return out.reshape(T, H * Dv) @ w[prefix + "o"].to(dt).T
 
 

@@ -195,6 +195,120 @@ def test_mixture_of_experts_part(dtype, T, E, top, ff, d):
     assert torch.allclose(base - 1.0, out, atol=1e-5 * float(out.abs().max()))
 
 
+def _paged_case(nh, nkv, hd, hdv, lens, new, dtype, seed, scale, cap, window):
+    """Random q, k, v of sequences with the given lengths laid into scrambled pages; the last ``new[b]`` positions
+    of each are the step's queries.  Keys and values get page pools of their own sizes."""
+    from test_kernels_gpu import DEV, Paged
+    g = torch.Generator().manual_seed(seed)
+    qs = [torch.randn(l, nh, hd, generator=g).to(dtype) for l in lens]
+    ks = [torch.randn(l, nkv, hd, generator=g).to(dtype) for l in lens]
+    vs = [torch.randn(l, nkv, hdv, generator=g).to(dtype) for l in lens]
+    pk, pv = Paged(lens, nkv, hd, dtype, seed), Paged(lens, nkv, hdv, dtype, seed)       # same seed: same block table
+    pk.fill(ks, ks)
+    pv.fill(vs, vs)
+    ref = torch.cat([P.attention_core(q.double(), k.double(), v.double(), scale, cap, window)[l - n:]
+                     for q, k, v, l, n in zip(qs, ks, vs, lens, new)]).reshape(sum(new), nh * hdv)
+    q = torch.cat([q[l - n:] for q, l, n in zip(qs, lens, new)]).reshape(sum(new), nh * hd).to(DEV)
+    seq = torch.from_numpy(np.repeat(np.arange(len(lens)), new).astype(np.int32)).to(DEV)
+    pos = torch.from_numpy(np.concatenate([np.arange(l - n, l) for l, n in zip(lens, new)]).astype(np.int32)).to(DEV)
+    cu = torch.from_numpy(np.concatenate([[0], np.cumsum(new)]).astype(np.int32)).to(DEV)
+    return dict(q=q, k=pk.dev()[0], v=pv.dev()[0], tab=pk.dev()[2], ref=ref, seq=seq, pos=pos, cu=cu,
+                lens=torch.tensor(lens, dtype=torch.int32, device=DEV))
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("nh,nkv,hd,hdv,cap,window", [(4, 2, 16, 24, 3.0, 9), (3, 3, 32, 8, 0.0, 70), (6, 1, 48, 48, 1.5, 0),
+                                                      (2, 1, 8, 130, 20.0, 64)])
+def test_attention_with_capped_scores_and_its_own_value_size(dtype, nh, nkv, hd, hdv, cap, window):
+    from ithaca_b200.csrc import ops
+    lens, new = [1, 70, 200, 129], [1, 70, 3, 1]
+    c = _paged_case(nh, nkv, hd, hdv, lens, new, dtype, 40, 0.7, cap or None, window or None)
+    status = torch.zeros(1, dtype=torch.int32, device="cuda")
+    got = ops.attention_simt(c["q"], c["k"], c["v"], c["seq"], c["pos"], c["tab"], nh, 0.7, window, status, softcap=cap)
+    assert status.item() == 0 and got.shape == (sum(new), nh * hdv)
+    assert rel_err(got.float().cpu().numpy(), c["ref"].numpy()) < (3e-6 if dtype == torch.float32 else 8e-3)
+
+
+@pytest.mark.parametrize("nh,nkv,hd,kind", [(4, 4, 16, "mma"), (6, 2, 32, "mma"), (8, 2, 64, "tc"), (8, 4, 128, "tc"), (6, 2, 128, "mma")])
+@pytest.mark.parametrize("cap,window", [(2.0, 0), (50.0, 72), (0.5, 40)])
+def test_tensor_core_attention_with_capped_scores(nh, nkv, hd, kind, cap, window):
+    """Prefill (both kernels) and decode.  The scale makes raw scores of several units, so a cap of 0.5 or 2 bends most
+    of them and a missing cap would show."""
+    from ithaca_b200.csrc import attention_bf16 as A
+    scale = 3.0 / hd ** 0.5
+    lens, new = [1, 70, 200, 129, 64, 700], [1, 70, 67, 129, 5, 450]
+    c = _paged_case(nh, nkv, hd, hd, lens, new, torch.bfloat16, 41, scale, cap, window or None)
+    status = torch.zeros(1, dtype=torch.int32, device="cuda")
+    got = A.prefill(c["q"], c["k"], c["v"], c["cu"], c["lens"], c["tab"], len(lens), max(new), nh, scale, window, status,
+                    kind=kind, softcap=cap)
+    assert status.item() == 0
+    assert rel_err(got.float().cpu().numpy(), c["ref"].numpy()) < 8e-3
+    lens = [1, 70, 200, 129, 64, 700]
+    d = _paged_case(nh, nkv, hd, hd, lens, [1] * len(lens), torch.bfloat16, 42, scale, cap, window or None)
+    for chunk in (1, 4):
+        got = A.decode(d["q"], d["k"], d["v"], d["lens"], d["tab"], len(lens), max(lens), nh, scale, window, status,
+                       chunk_pages=chunk, softcap=cap)
+        assert status.item() == 0
+        assert rel_err(got.float().cpu().numpy(), d["ref"].numpy()) < 8e-3
+    # the test has teeth: without the cap the result is another one
+    if cap <= 2.0:
+        free = A.decode(d["q"], d["k"], d["v"], d["lens"], d["tab"], len(lens), max(lens), nh, scale, window, status)
+        assert rel_err(free.float().cpu().numpy(), d["ref"].numpy()) > 5e-2
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("taps,rot,pairing,hd,hdv", [(3, 8, 1, 16, 24), (4, 16, 0, 16, 16), (1, 0, 1, 8, 8), (2, 32, 1, 32, 8), (0, 8, 1, 16, 24)])
+def test_convolution_rotation_append_kernel(dtype, taps, rot, pairing, hd, hdv):
+    """Three sequences fed in two steps (the second reads the first's last values from the ring, for one sequence a
+    single new token, for one more tokens than taps) against the plain convolution and rotation of the whole sequences."""
+    from test_kernels_gpu import DEV, Paged
+    from ithaca_b200.csrc import ops
+    nh, nkv = 4, 2
+    ctot = (nh + nkv) * hd + nkv * hdv
+    total, first = [70, 9, 131], [67, 8, 60]
+    g = torch.Generator().manual_seed(taps * 7 + rot)
+    u = [torch.randn(l, ctot, generator=g) for l in total]
+    w = torch.randn(ctot, max(taps, 1), generator=g)
+    freqs = P.rotary_frequencies(rot, 100.0, None) if rot else None
+    pk, pv = Paged(total, nkv, hd, dtype, 3), Paged(total, nkv, hdv, dtype, 3)
+    k_d, v_d, tab = pk.dev()[0], pv.dev()[0], pk.dev()[2]
+    slots = torch.tensor([2, 0, 5], dtype=torch.int32, device=DEV)
+    ring = torch.full((6, taps, ctot), 9.0, device=DEV) if taps > 1 else None          # what an earlier user left there
+    inv = torch.tensor(freqs.numpy(), dtype=torch.float32, device=DEV) if rot else None
+    status = torch.zeros(1, dtype=torch.int32, device=DEV)
+    q_got = [[] for _ in total]
+    for lo, hi in ([0] * 3, first), (first, total):
+        new = [h - l for l, h in zip(lo, hi)]
+        qkv = torch.cat([x[l:h] for x, l, h in zip(u, lo, hi)]).to(DEV)
+        seq = torch.from_numpy(np.repeat(np.arange(3), new).astype(np.int32)).to(DEV)
+        pos = torch.from_numpy(np.concatenate([np.arange(l, h) for l, h in zip(lo, hi)]).astype(np.int32)).to(DEV)
+        cu = torch.from_numpy(np.concatenate([[0], np.cumsum(new)]).astype(np.int32)).to(DEV)
+        q_out = torch.empty(sum(new), nh * hd, dtype=dtype, device=DEV)
+        ops.conv_rope_append(qkv, w.to(DEV) if taps else None, ring, slots, cu, torch.tensor(hi, dtype=torch.int32, device=DEV),
+                             q_out, k_d, v_d, seq, pos, tab, inv, nh, nkv, rot, pairing, True, status)
+        for b, part in enumerate(torch.split(q_out.float().cpu(), new)):
+            q_got[b].append(part)
+    assert status.item() == 0
+    tol = 3e-6 if dtype == torch.float32 else 8e-3
+    for b, l in enumerate(total):
+        y = P.short_conv(u[b].double(), w.double()) if taps else u[b].double()
+        q = y[:, :nh * hd].reshape(l, nh, hd)
+        k = y[:, nh * hd:(nh + nkv) * hd].reshape(l, nkv, hd)
+        v = y[:, (nh + nkv) * hd:].reshape(l, nkv, hdv)
+        if rot:
+            if pairing == 0:                                   # pairs (i, i + rot/2): bring them side by side, turn, and back
+                order = torch.stack((torch.arange(rot // 2), torch.arange(rot // 2) + rot // 2), 1).reshape(-1)
+                back = torch.argsort(order)
+                turn = lambda x: torch.cat((P.rotate_pairs(x[..., order], range(l), freqs)[..., back], x[..., rot:]), -1)
+                q, k = turn(q), turn(k)
+            else:
+                q, k = P.rotate_pairs(q, range(l), freqs), P.rotate_pairs(k, range(l), freqs)
+        assert rel_err(torch.cat(q_got[b]).numpy(), q.reshape(l, -1).numpy()) < tol
+        kk = torch.stack([k_d.cpu()[pk.table[b, j // 64], :, j % 64] for j in range(l)]).float()
+        vv = torch.stack([v_d.cpu()[pk.table[b, j // 64], :, j % 64] for j in range(l)]).float()
+        assert rel_err(kk.numpy(), k.numpy()) < tol and rel_err(vv.numpy(), v.numpy()) < tol
+
+
 # ------------------------------------------------------------------------------------------ whole models
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 @pytest.mark.parametrize("name", ["A", "B"])
