@@ -91,6 +91,7 @@ inline size_t stream_k_bytes() { return SK_FLAG_INTS * 4 + (size_t)max_blocks() 
 // One accumulator's worth of work: K steps [kb0, kb0 + nkb) of output tile (nt, mt).
 struct Work {
     int tile, mt, nt, z, kb0, nkb;
+    int group = 0;                    // grouped products: which of the stacked weight matrices this token tile multiplies
     bool first, last;                 // holds the tile's first / last K step
 };
 
@@ -101,6 +102,9 @@ struct Walk {
     int tiles_m, tiles_n, nkb_total, kb_per_split;
     int item, n_items;                // data-parallel: items blockIdx.x, + gridDim.x, ...; item -> (K slice, weight tile, token tile)
     long long u, u_end, n_units;      // stream-K: this block's share [u, u_end) of all (tile, K step) units, token tile fastest
+    // grouped products (whole tiles only): groups[mt] = the weight matrix of token tile mt, or -1 for a token tile that
+    // holds nothing and is passed over.  Written by the kernel before: read after the wait for it, with a load that stays there.
+    const int* groups = nullptr;
     __device__ Walk(bool sk_, int tm, int tn, int nkb, int per, int n_splits)
         : sk(sk_), tiles_m(tm), tiles_n(tn), nkb_total(nkb), kb_per_split(per), item(blockIdx.x), n_items(tm * tn * n_splits),
           n_units((long long)tm * tn * nkb) {
@@ -136,12 +140,18 @@ struct Walk {
             w.z = 0;
             u += w.nkb;
         } else {
-            if (item >= n_items) return false;
-            w.tile = item % (tiles_m * tiles_n);
-            w.z = item / (tiles_m * tiles_n);
+            for (;;) {
+                if (item >= n_items) return false;
+                w.tile = item % (tiles_m * tiles_n);
+                w.z = item / (tiles_m * tiles_n);
+                item += gridDim.x;
+                if (!groups) break;
+                int g;
+                asm volatile("ld.global.s32 %0, [%1];" : "=r"(g) : "l"(groups + w.tile % tiles_m) : "memory");
+                if (g >= 0) { w.group = g; break; }
+            }
             w.kb0 = w.z * kb_per_split;
             w.nkb = min(kb_per_split, nkb_total - w.kb0);
-            item += gridDim.x;
         }
         w.mt = w.tile % tiles_m;
         w.nt = w.tile / tiles_m;
@@ -212,7 +222,10 @@ template <int BN, typename TY, int MODE>
 __global__ void __launch_bounds__(THREADS, 1)
 gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_x,
                     TY* __restrict__ Y, float* __restrict__ partial, int M, int N, int K, int ldy, int accumulate,
-                    int swiglu, int kb_per_split, int n_splits, int stream_k, int* status, const IkRopeStore rope, int bn) {
+                    int swiglu, int kb_per_split, int n_splits, int stream_k, int* status, const IkRopeStore rope, int bn,
+                    const int* tile_group) {
+    // tile_group != nullptr: a grouped product.  W stacks several [N, K] matrices; token tile mt multiplies matrix
+    // tile_group[mt] (rows group * N ... of W), and token tiles marked -1 are passed over.
     // bn <= BN: the width of a token tile in use (a multiple of 16): tiles lie bn tokens apart, bn rows of tokens are
     // loaded per stage and the products are bn columns wide; BN is the room a stage and an accumulator have.
     typedef Cfg<BN> C;
@@ -263,11 +276,12 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
     walk_first.cl = CL;
     walk_first.pairs = PAIRS;
     if (PAIRS) walk_first.item = blockIdx.x / 2;
+    walk_first.groups = tile_group;
     const Walk walk_init = walk_first;
     // Weights are written by no kernel: the first stages' weight tiles are asked for before the wait for the kernel
     // before this one (whose results are the tokens), so a product launched early has them on the way by then.
     int pre_issued = 0;
-    if (threadIdx.x == 0) {
+    if (threadIdx.x == 0 && !tile_group) {             // (a grouped product learns its weight tiles from the kernel before)
         Walk walk = walk_init;
         for (Work w; pre_issued < NST && walk.next(w);)
             for (int i = 0; i < w.nkb && pre_issued < NST; i += KSUB, pre_issued++) {
@@ -292,7 +306,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
             bool ok = true;
             Walk walk = walk_init;
             for (Work w; ok && walk.next(w);) {
-                const int n0 = w.nt * BM, m0 = w.mt * bn, kb0 = w.kb0, nkb = w.nkb;
+                const int n0 = w.nt * BM + w.group * N, m0 = w.mt * bn, kb0 = w.kb0, nkb = w.nkb;       // n0: the weight tile's first row in W
                 for (int i = 0; i < nkb; i += KSUB, it++) {
                     const int s = it % NST, n_sub = min(KSUB, nkb - i);
                     unsigned char* a = tiles + s * STAGE;
@@ -668,6 +682,7 @@ template <int BN, typename TY>
 int launch_cluster(const CUtensorMap& mw, const CUtensorMap& mx, void* Y, int M, int N, int K, int ldy, int accumulate,
                    int swiglu, int n_cl, int* status, const IkRopeStore& rope, int bn, cudaStream_t stream) {
     typedef Cfg<BN> C;
+    const int* groups = nullptr;
     if (C::RED_SLOTS == 0) return IK_UNSUPPORTED;
     const int nkb = (K + BK - 1) / BK;
     const long long tiles = (long long)((N + BM - 1) / BM) * ((M + bn - 1) / bn);
@@ -689,14 +704,16 @@ int launch_cluster(const CUtensorMap& mw, const CUtensorMap& mx, void* Y, int M,
     cfg.attrs = attr;
     cfg.numAttrs = (ik_pdl_mask() & IK_FAMILY) ? 2 : 1;
     IK_RETURN_IF_ERROR(cudaLaunchKernelEx(&cfg, kern, mw, mx, (TY*)Y, (float*)nullptr, M, N, K, ldy, accumulate, swiglu, per, n_cl, 0,
-                                          status, rope, bn));
+                                          status, rope, bn, groups));
     return (int)cudaGetLastError();
 }
 
 template <int BN, typename TY>
 int launch(const CUtensorMap& mw, const CUtensorMap& mx, void* Y, float* partial, int M, int N, int K, int ldy,
-           int accumulate, int swiglu, int splits, int* status, const IkRopeStore& rope, int bn, cudaStream_t stream) {
+           int accumulate, int swiglu, int splits, int* status, const IkRopeStore& rope, int bn, cudaStream_t stream,
+           const int* groups = nullptr) {
     typedef Cfg<BN> C;
+    if (groups && splits != 1) return IK_BAD_ARGUMENT;
     if (splits < 0) return launch_cluster<BN, TY>(mw, mx, Y, M, N, K, ldy, accumulate, swiglu, -splits, status, rope, bn, stream);
     auto kern = gemm_tcgen05_kernel<BN, TY, 0>;
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM);
@@ -707,24 +724,24 @@ int launch(const CUtensorMap& mw, const CUtensorMap& mx, void* Y, float* partial
         const long long units = tiles * nkb;
         const int blocks = (int)(units / 4 < 1 ? 1 : units / 4 < max_blocks() ? units / 4 : max_blocks());
         IK_RETURN_IF_ERROR(ik_launch(kern, blocks, THREADS, C::SMEM, stream, mw, mx, (TY*)Y, partial, M, N, K, ldy, accumulate,
-                                     swiglu, nkb, 1, 1, status, rope, bn));
+                                     swiglu, nkb, 1, 1, status, rope, bn, groups));
         return (int)cudaGetLastError();
     }
     const int per = (nkb + splits - 1) / splits;
     const int n_splits = (nkb + per - 1) / per;
     const long long total = tiles * n_splits;
     const int blocks = (int)(total < max_blocks() ? total : max_blocks());
-    if (n_splits == 1 && BN <= 128 && M > 128) {
+    if (n_splits == 1 && BN <= 128 && M > 128 && (!groups || bn >= 64)) {
         // whole narrow tiles of a product with several token tiles (compute-bound, few weight tiles): two K blocks a stage
         auto kern2 = gemm_tcgen05_kernel<BN <= 128 ? BN : 128, TY, 3>;
         e = cudaFuncSetAttribute(kern2, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM);
         if (e != cudaSuccess) return (int)e;
         IK_RETURN_IF_ERROR(ik_launch(kern2, blocks, THREADS, C::SMEM, stream, mw, mx, (TY*)Y, (float*)nullptr, M, N, K, ldy, accumulate,
-                                     swiglu, per, 1, 0, status, rope, bn));
+                                     swiglu, per, 1, 0, status, rope, bn, groups));
         return (int)cudaGetLastError();
     }
     IK_RETURN_IF_ERROR(ik_launch(kern, blocks, THREADS, C::SMEM, stream, mw, mx, (TY*)Y, n_splits > 1 ? partial : nullptr, M,
-                                 N, K, ldy, accumulate, swiglu, per, n_splits, 0, status, rope, bn));
+                                 N, K, ldy, accumulate, swiglu, per, n_splits, 0, status, rope, bn, groups));
     e = cudaGetLastError();
     if (e != cudaSuccess) return (int)e;
     if (n_splits > 1) {
@@ -770,6 +787,7 @@ template <typename TY>
 int launch_pairs(const CUtensorMap& mw, const CUtensorMap& mx_half, void* Y, int M, int N, int K, int ldy, int accumulate,
                  int swiglu, int* status, const IkRopeStore& rope, int bn, cudaStream_t stream) {
     typedef Cfg<256> C;
+    const int* groups = nullptr;
     auto kern = gemm_tcgen05_kernel<256, TY, 2>;
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM);
     if (e != cudaSuccess) return (int)e;
@@ -790,7 +808,7 @@ int launch_pairs(const CUtensorMap& mw, const CUtensorMap& mx_half, void* Y, int
     cfg.attrs = attr;
     cfg.numAttrs = (ik_pdl_mask() & IK_FAMILY) ? 2 : 1;
     IK_RETURN_IF_ERROR(cudaLaunchKernelEx(&cfg, kern, mw, mx_half, (TY*)Y, (float*)nullptr, M, N, K, ldy, accumulate, swiglu, nkb, 1, 0,
-                                          status, rope, bn));
+                                          status, rope, bn, groups));
     return (int)cudaGetLastError();
 }
 
@@ -837,7 +855,8 @@ IK_EXPORT int ik_gemm_tcgen05_stream_k_bytes() { return (int)stream_k_bytes(); }
 // swiglu: W holds (gate j, up j) in rows (2j, 2j + 1); Y is [M, N / 2] = silu(gate) * up.
 static int gemm_tcgen05_impl(const void* X, const void* W, void* Y, int y_dtype, float* partial, int M, int N, int K,
                              int ldx, int ldw, int ldy, int accumulate, int swiglu, int splits, int* status,
-                             const IkRopeStore& rope, cudaStream_t stream) {
+                             const IkRopeStore& rope, cudaStream_t stream, const int* groups = nullptr, int n_groups = 1,
+                             int bn_given = 0) {
     if (M < 0 || N <= 0 || K <= 0 || ldx < K || ldw < K || (!rope.q_out && ldy < (swiglu ? N / 2 : N)))
         return IK_BAD_ARGUMENT;
     if (swiglu && ((N & 1) || accumulate)) return IK_BAD_ARGUMENT;
@@ -846,15 +865,16 @@ static int gemm_tcgen05_impl(const void* X, const void* W, void* Y, int y_dtype,
     if (splits != 1 && splits >= 0 && !partial) return IK_BAD_ARGUMENT;
     if (M == 0) return IK_OK;
     if (splits < 0 && M > 128) return IK_UNSUPPORTED;     // the cluster mode is for one token tile of at most 128 tokens
-    const int bn = ik_gemm_tcgen05_tile_width(M, N), room = ik_gemm_tcgen05_tile(bn);
+    if (groups && (n_groups < 1 || bn_given < 16 || bn_given > 256 || bn_given % 16 || splits != 1 || rope.q_out)) return IK_BAD_ARGUMENT;
+    const int bn = groups ? bn_given : ik_gemm_tcgen05_tile_width(M, N), room = ik_gemm_tcgen05_tile(bn);
     CUtensorMap mw, mx;
-    int st = ik_make_map(&mw, W, N, K, ldw, BM);
+    int st = ik_make_map(&mw, W, (unsigned long long)N * (groups ? n_groups : 1), K, ldw, BM);
     if (st != IK_OK) return st;
     st = ik_make_map(&mx, X, M, K, ldx, bn);
     if (st != IK_OK) return st;
 #define IK_TC(BN_)                                                                                                       \
-    return y_dtype == IK_F32 ? launch<BN_, float>(mw, mx, Y, partial, M, N, K, ldy, accumulate, swiglu, splits, status, rope, bn, stream) \
-                             : launch<BN_, bf16>(mw, mx, Y, partial, M, N, K, ldy, accumulate, swiglu, splits, status, rope, bn, stream)
+    return y_dtype == IK_F32 ? launch<BN_, float>(mw, mx, Y, partial, M, N, K, ldy, accumulate, swiglu, splits, status, rope, bn, stream, groups) \
+                             : launch<BN_, bf16>(mw, mx, Y, partial, M, N, K, ldy, accumulate, swiglu, splits, status, rope, bn, stream, groups)
     switch (room) {
         case 32: IK_TC(32);
         case 64: IK_TC(64);
@@ -869,6 +889,18 @@ IK_EXPORT int ik_gemm_tcgen05(const void* X, const void* W, void* Y, int y_dtype
                               cudaStream_t stream) {
     IkRopeStore none = {};
     return gemm_tcgen05_impl(X, W, Y, y_dtype, partial, M, N, K, ldx, ldw, ldy, accumulate, swiglu, splits, status, none, stream);
+}
+
+// A grouped product: W stacks n_groups matrices [N, K]; the M rows of X lie in token tiles of `bn` rows (a multiple of 16
+// up to 256), and token tile i multiplies matrix tile_group[i] (device ints, one per tile; -1 = the tile holds nothing and
+// is passed over).  Whole tiles dealt round robin; everything else as ik_gemm_tcgen05.
+IK_EXPORT int ik_gemm_tcgen05_grouped(const void* X, const void* W, void* Y, int y_dtype, const int* tile_group, int n_groups,
+                                      int bn, int M, int N, int K, int ldx, int ldw, int ldy, int swiglu, int* status,
+                                      cudaStream_t stream) {
+    IkRopeStore none = {};
+    if (!tile_group || M % (bn > 0 ? bn : 1)) return IK_BAD_ARGUMENT;
+    return gemm_tcgen05_impl(X, W, Y, y_dtype, nullptr, M, N, K, ldx, ldw, ldy, 0, swiglu, 1, status, none, stream, tile_group,
+                             n_groups, bn);
 }
 
 // The fused q/k/v product with the rotary / cache epilogue (rope_store.cuh).  N must be (nh + 2 nkv) * hd, hd even.

@@ -13,6 +13,12 @@
 //             CUDA cores, float accumulation in ascending k per output element: a row's result does not depend on
 //             its place in a tile nor on what else is in the step.
 //   combine   y[t] = sum_k weight[t, k] * out[t * top + k], ascending k.
+//
+// The bfloat16 path runs the two products on the tcgen05 product's grouped mode instead (gemm_tcgen05.cu).  For that
+// the sort lays the assignments out in padded order: every expert's rows start at a multiple of the token tile's
+// height, so that a token tile belongs to one expert (sort_padded: row_of[a], the row of assignment a; src_token[r], the
+// token whose activations row r holds, -1 for padding; tile_group[i], the expert of tile i, -1 for unused tiles), a
+// gather copies the tokens' activations into that order (padding rows zero), and combine follows row_of.
 #include <math.h>
 #define IK_FAMILY 2
 #include "common.cuh"
@@ -142,7 +148,7 @@ moe_gemm_kernel(const TX* __restrict__ X, const TW* __restrict__ W, TY* __restri
     const int e = tiles[2 * blockIdx.y], p0 = tiles[2 * blockIdx.y + 1];
     const int rows = min(MOE_BM, offsets[e + 1] - p0);
     const int n0 = blockIdx.x * MOE_BN;
-    // expert e's matrix: mode 0 [2N, K] (gate rows, then up rows), mode 1 [N, K]
+    // expert e's matrix: mode 0 [2N, K] (gate j in row 2j, up j in row 2j + 1), mode 1 [N, K]
     const TW* We = W + (size_t)e * (MODE == 0 ? 2 : 1) * N * K;
     if (threadIdx.x < MOE_BM) {
         const int r = threadIdx.x;
@@ -168,7 +174,7 @@ moe_gemm_kernel(const TX* __restrict__ X, const TW* __restrict__ W, TY* __restri
             xs[c][r] = (sr >= 0 && k < K) ? ik_ld(X, (size_t)sr * ldx + k) : 0.f;
             #pragma unroll
             for (int w = 0; w < NW; w++)
-                ws[w][c][r] = (n0 + r < N && k < K) ? ik_ld(We, ((size_t)w * N + n0 + r) * K + k) : 0.f;
+                ws[w][c][r] = (n0 + r < N && k < K) ? ik_ld(We, ((size_t)(MODE == 0 ? 2 : 1) * (n0 + r) + w) * K + k) : 0.f;
         }
         __syncthreads();
         #pragma unroll
@@ -203,19 +209,71 @@ moe_gemm_kernel(const TX* __restrict__ X, const TW* __restrict__ W, TY* __restri
     }
 }
 
+// ------------------------------------------------------------------------------------------ padded order
+// One block.  row_of [A], src_token [n_tiles * bn], tile_group [n_tiles].
+__global__ void __launch_bounds__(1024)
+moe_sort_padded_kernel(const int* __restrict__ chosen, int* __restrict__ row_of, int* __restrict__ src_token,
+                       int* __restrict__ tile_group, int A, int E, int top, int bn, int n_tiles) {
+    ik_pdl_wait();
+    IK_AFTER_WAIT(chosen);
+    ik_pdl_launch_dependents();
+    extern __shared__ int cnt[];         // [E] counts, then [E] cursors
+    int* cur = cnt + E;
+    for (int e = threadIdx.x; e < E; e += blockDim.x) cnt[e] = 0;
+    for (int r = threadIdx.x; r < n_tiles * bn; r += blockDim.x) src_token[r] = -1;
+    __syncthreads();
+    for (int a = threadIdx.x; a < A; a += blockDim.x) {
+        const int e = chosen[a];
+        if (e >= 0 && e < E) atomicAdd(&cnt[e], 1);
+    }
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        int nt = 0;
+        for (int e = 0; e < E; e++) {
+            cur[e] = nt * bn;
+            for (int r = 0; r < cnt[e] && nt < n_tiles; r += bn) tile_group[nt++] = e;
+        }
+        for (; nt < n_tiles; nt++) tile_group[nt] = -1;
+    }
+    __syncthreads();
+    for (int a = threadIdx.x; a < A; a += blockDim.x) {
+        const int e = chosen[a];
+        if (e < 0 || e >= E) { row_of[a] = 0; continue; }
+        const int r = atomicAdd(&cur[e], 1);
+        row_of[a] = r;
+        if (r < n_tiles * bn) src_token[r] = a / top;
+    }
+}
+
+// xp[r, :] = x[src_token[r], :], zeros where src_token[r] < 0; rows of d bfloat16, d a multiple of 8
+__global__ void moe_gather_kernel(const uint4* __restrict__ x, const int* __restrict__ src_token, uint4* __restrict__ xp,
+                                  int rows, int d8) {
+    ik_pdl_wait();
+    IK_AFTER_WAIT(x);
+    IK_AFTER_WAIT(src_token);
+    ik_pdl_launch_dependents();
+    const size_t total = (size_t)rows * d8, stride = (size_t)gridDim.x * blockDim.x;
+    for (size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x; idx < total; idx += stride) {
+        const size_t r = idx / d8;
+        const int c = (int)(idx - r * d8), t = src_token[r];
+        xp[idx] = t >= 0 ? x[(size_t)t * d8 + c] : make_uint4(0u, 0u, 0u, 0u);
+    }
+}
+
 // ------------------------------------------------------------------------------------------ combine
-__global__ void moe_combine_kernel(const float* __restrict__ parts, const float* __restrict__ weight, float* __restrict__ y,
-                                   int T, int top, int d) {
+__global__ void moe_combine_kernel(const float* __restrict__ parts, const float* __restrict__ weight, const int* __restrict__ row_of,
+                                   float* __restrict__ y, int T, int top, int d) {
     ik_pdl_wait();
     IK_AFTER_WAIT(parts);
     IK_AFTER_WAIT(weight);
+    IK_AFTER_WAIT(row_of);
     ik_pdl_launch_dependents();
     const size_t total = (size_t)T * d, stride = (size_t)gridDim.x * blockDim.x;
     for (size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x; idx < total; idx += stride) {
         const size_t t = idx / d;
         const int i = (int)(idx - t * d);
         float acc = 0.f;
-        for (int k = 0; k < top; k++) acc = fmaf(weight[t * top + k], parts[(t * top + k) * d + i], acc);
+        for (int k = 0; k < top; k++) acc = fmaf(weight[t * top + k], parts[(size_t)(row_of ? row_of[t * top + k] : t * top + k) * d + i], acc);
         y[idx] = acc;
     }
 }
@@ -262,7 +320,7 @@ IK_EXPORT int ik_moe_sort(const int* chosen, int* offsets, int* sorted, int* til
     IK_LAUNCH_STATUS();
 }
 
-// mode 0: X [T, K] tokens, W [E, 2N, K], Y [A, N] = silu(gate) * up at sorted places.  mode 1: X [A, K] at sorted
+// mode 0: X [T, K] tokens, W [E, 2N, K] (gate j, up j in rows 2j, 2j + 1), Y [A, N] = silu(gate) * up at sorted places.  mode 1: X [A, K] at sorted
 // places, W [E, N, K], Y [A, N] at the assignments' rows.
 IK_EXPORT int ik_moe_gemm(int mode, const void* X, int x_dtype, const void* W, int w_dtype, void* Y, int y_dtype,
                           const int* offsets, const int* sorted, const int* tiles, const int* n_tiles, int max_tiles, int top,
@@ -274,10 +332,28 @@ IK_EXPORT int ik_moe_gemm(int mode, const void* X, int x_dtype, const void* W, i
     return IK_BAD_ARGUMENT;
 }
 
-IK_EXPORT int ik_moe_combine(const float* parts, const float* weight, float* y, int T, int top, int d, cudaStream_t stream) {
+IK_EXPORT int ik_moe_sort_padded(const int* chosen, int* row_of, int* src_token, int* tile_group, int A, int E, int top, int bn,
+                                 int n_tiles, cudaStream_t stream) {
+    if (A < 0 || E <= 0 || top <= 0 || bn <= 0 || n_tiles < 0 || n_tiles < (A / bn + E < A ? A / bn + E : A)) return IK_BAD_ARGUMENT;
+    if ((size_t)2 * E * sizeof(int) > 48 * 1024) return IK_UNSUPPORTED;
+    IK_RETURN_IF_ERROR(ik_launch(moe_sort_padded_kernel, 1, 1024, (size_t)2 * E * sizeof(int), stream, chosen, row_of, src_token, tile_group, A, E,
+                                 top, bn, n_tiles));
+    IK_LAUNCH_STATUS();
+}
+
+IK_EXPORT int ik_moe_gather(const void* x, const int* src_token, void* xp, int rows, int d, cudaStream_t stream) {
+    if (rows < 0 || d <= 0 || d % 8 || ((uintptr_t)x % 16) || ((uintptr_t)xp % 16)) return IK_BAD_ARGUMENT;
+    if (rows == 0) return IK_OK;
+    const size_t total = (size_t)rows * (d / 8), want = (total + 255) / 256, cap = (size_t)ik_sm_count() * 16;
+    IK_RETURN_IF_ERROR(ik_launch(moe_gather_kernel, (int)(want < cap ? want : cap), 256, 0, stream, (const uint4*)x, src_token, (uint4*)xp, rows, d / 8));
+    IK_LAUNCH_STATUS();
+}
+
+// row_of: where assignment a's result lies in `parts` (nullptr: at row a)
+IK_EXPORT int ik_moe_combine(const float* parts, const float* weight, const int* row_of, float* y, int T, int top, int d, cudaStream_t stream) {
     if (T < 0 || top <= 0 || d <= 0) return IK_BAD_ARGUMENT;
     if (T == 0) return IK_OK;
     const size_t total = (size_t)T * d, want = (total + 255) / 256, cap = (size_t)ik_sm_count() * 16;
-    IK_RETURN_IF_ERROR(ik_launch(moe_combine_kernel, (int)(want < cap ? want : cap), 256, 0, stream, parts, weight, y, T, top, d));
+    IK_RETURN_IF_ERROR(ik_launch(moe_combine_kernel, (int)(want < cap ? want : cap), 256, 0, stream, parts, weight, row_of, y, T, top, d));
     IK_LAUNCH_STATUS();
 }

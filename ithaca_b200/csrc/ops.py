@@ -93,7 +93,10 @@ _SIGNATURES = {
     "ik_moe_route": [_vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _vp],
     "ik_moe_sort": [_vp, _vp, _vp, _vp, _vp, _i, _i, _i, _vp],
     "ik_moe_gemm": [_i, _vp, _i, _vp, _i, _vp, _i, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _vp],
-    "ik_moe_combine": [_vp, _vp, _vp, _i, _i, _i, _vp],
+    "ik_moe_combine": [_vp, _vp, _vp, _vp, _i, _i, _i, _vp],
+    "ik_moe_sort_padded": [_vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _vp],
+    "ik_moe_gather": [_vp, _vp, _vp, _i, _i, _vp],
+    "ik_gemm_tcgen05_grouped": [_vp, _vp, _vp, _i, _vp, _i, _i, _i, _i, _i, _i, _i, _i, _i, _vp, _vp],
     "ik_argmax": [_vp, _i, _vp, _i, _i, _vp, _vp],
     "ik_argmax_scratch_bytes": [],
     "ik_selftest_wait_expires": [_vp, _vp, _vp, _u64, _vp],
@@ -691,7 +694,7 @@ def moe_sort(chosen: torch.Tensor, n_experts: int) -> MoEPlan:
 
 
 def moe_gemm(mode: int, x: torch.Tensor, w: torch.Tensor, plan: MoEPlan, out_dtype: torch.dtype) -> torch.Tensor:
-    """Mode 0: ``x`` [T, d] tokens, ``w`` [E, 2 ff, d] (gate rows then up rows) -> silu(gate) * up [A, ff] in sorted
+    """Mode 0: ``x`` [T, d] tokens, ``w`` [E, 2 ff, d] (gate j and up j in rows 2j and 2j + 1) -> silu(gate) * up [A, ff] in sorted
     order.  Mode 1: ``x`` [A, ff] in sorted order, ``w`` [E, d, ff] -> [A, d], row t * top + k for token t's choice k."""
     _need(x, "x")
     _need(w, "w")
@@ -709,18 +712,76 @@ def moe_gemm(mode: int, x: torch.Tensor, w: torch.Tensor, plan: MoEPlan, out_dty
     return out
 
 
-def moe_combine(parts: torch.Tensor, weight: torch.Tensor, out: Optional[torch.Tensor] = None) -> torch.Tensor:
-    """y[t] = sum_k weight[t, k] * parts[t * top + k]."""
+class MoEPaddedPlan:
+    """A step's (token, choice) pairs in padded order: every expert's rows start at a multiple of the tile height."""
+    __slots__ = ("row_of", "src_token", "tile_group", "n_tiles", "bn", "rows", "top", "n_experts")
+
+
+def moe_sort_padded(chosen: torch.Tensor, n_experts: int, bn: int) -> MoEPaddedPlan:
+    _need(chosen, "chosen", torch.int32)
+    T, top = chosen.shape
+    A = T * top
+    p = MoEPaddedPlan()
+    p.top, p.n_experts, p.bn = top, n_experts, bn
+    p.n_tiles = min(A, A // bn + n_experts)              # a tile holds at least one row; an expert wastes less than one tile
+    p.rows = p.n_tiles * bn
+    meta = torch.empty(A + p.rows + p.n_tiles, dtype=torch.int32, device=chosen.device)
+    p.row_of, p.src_token, p.tile_group = meta[:A], meta[A:A + p.rows], meta[A + p.rows:]
+    _work(f"moe_sort_padded {A}", 8 * A + 4 * p.rows)
+    _check(lib().ik_moe_sort_padded(_ptr(chosen), _ptr(p.row_of), _ptr(p.src_token), _ptr(p.tile_group), A, n_experts, top, bn,
+                                    p.n_tiles, _stream()), "moe_sort_padded")
+    return p
+
+
+def moe_gather(x: torch.Tensor, plan: MoEPaddedPlan) -> torch.Tensor:
+    """The tokens' activations in padded order [rows, d] (bfloat16; padding rows zero)."""
+    _need(x, "x", torch.bfloat16)
+    d = x.shape[1]
+    out = torch.empty((plan.rows, d), dtype=torch.bfloat16, device=x.device)
+    _work(f"moe_gather {plan.rows}x{d}", 4 * plan.rows * d)
+    _check(lib().ik_moe_gather(_ptr(x), _ptr(plan.src_token), _ptr(out), plan.rows, d, _stream()), "moe_gather")
+    return out
+
+
+def gemm_tcgen05_grouped(x: torch.Tensor, w: torch.Tensor, plan: MoEPaddedPlan, out_dtype: torch.dtype, swiglu: bool = False,
+                         status: Optional[torch.Tensor] = None) -> Optional[torch.Tensor]:
+    """``x`` [rows, K] in padded order, ``w`` [E * N, K]: the stacked matrices of the experts; token tile i of ``plan.bn``
+    rows multiplies matrix ``plan.tile_group[i]``.  Returns [rows, N] (N / 2 with the SwiGLU epilogue; rows of unused
+    tiles are left as they are), or None when the tcgen05 kernel does not take these sizes."""
+    _need(x, "x", torch.bfloat16)
+    _need(w, "w", torch.bfloat16)
+    M, K = x.shape
+    N = w.shape[0] // plan.n_experts
+    if w.shape[1] != K or M != plan.rows or w.shape[0] != N * plan.n_experts:
+        raise KernelError("gemm_tcgen05_grouped: the sizes do not fit together")
+    if K % 8 or x.data_ptr() % 16 or w.data_ptr() % 16 or (swiglu and N % 2):
+        return None
+    n_out = N // 2 if swiglu else N
+    out = torch.empty((M, n_out), dtype=out_dtype, device=x.device)
+    used = min(M, plan.rows)
+    _work(f"gemm_tcgen05 grouped{' +swiglu' if swiglu else ''} {used}x{N}x{K}", 2 * (used * K + min(plan.n_experts, plan.n_tiles) * N * K) + used * n_out * out.element_size(),
+          2 * used * N * K)
+    st = lib().ik_gemm_tcgen05_grouped(_ptr(x), _ptr(w), _ptr(out), _code(out), _ptr(plan.tile_group), plan.n_experts, plan.bn,
+                                       M, N, K, x.stride(0), w.stride(0), out.stride(0), 1 if swiglu else 0, _ptr(status), _stream())
+    if st == -2:
+        return None
+    _check(st, "gemm_tcgen05_grouped")
+    return out
+
+
+def moe_combine(parts: torch.Tensor, weight: torch.Tensor, out: Optional[torch.Tensor] = None,
+                row_of: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """y[t] = sum_k weight[t, k] * parts[row_of[t * top + k]] (``row_of`` None: row t * top + k)."""
     _need(parts, "parts", torch.float32)
     _need(weight, "weight", torch.float32)
     T, top = weight.shape
     d = parts.shape[1]
-    if parts.shape[0] != T * top:
+    if row_of is None and parts.shape[0] != T * top:
         raise KernelError("moe_combine: one row per (token, choice) is needed")
     if out is None:
         out = torch.empty((T, d), dtype=torch.float32, device=parts.device)
     _work(f"moe_combine {T}x{d}", _nbytes(parts, out))
-    _check(lib().ik_moe_combine(_ptr(parts), _ptr(weight), _ptr(out), T, top, d, _stream()), "moe_combine")
+    _check(lib().ik_moe_combine(_ptr(parts), _ptr(weight), _ptr(row_of), _ptr(out), T, top, d, _stream()), "moe_combine")
     return out
 
 

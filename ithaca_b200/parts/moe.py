@@ -11,6 +11,13 @@ On the device: one kernel picks experts and weights per token; a counting sort g
 with silu(g) * u as its epilogue, so the [rows, 2 ff] intermediate is never written); a last kernel
 adds a token's choices in the order they were chosen.  Nothing is read back by the host: grids are
 sized from upper bounds, so a captured step can be replayed.
+
+The bfloat16 path's products are the tcgen05 product in its grouped mode: the pairs are laid out so
+that every expert's rows start at a multiple of the token tile's height, the tokens' activations are
+gathered into that order, and each token tile multiplies its expert's slice of the stacked weights.
+The tile height follows the rows an expert gets on average (16 for a decode step, up to 256 for a
+long prompt).  The float32 path, and sizes the tensor-core kernel does not take (widths that are no
+multiple of 8), run the CUDA-core grouped product.
 """
 from __future__ import annotations
 
@@ -71,21 +78,40 @@ class MoEFeedForward:
             t = torch.stack([to_device(m, runtime) for m in mats], dim=0)
             return (t.to(wt) if wt is not None else t).contiguous()
 
-        self.gate_up = stack([torch.cat((tensors[g], tensors[u]), dim=0) for g, u, _ in experts])     # [E, 2 ff, d]
+        # gate j and up j in rows 2j and 2j + 1, so that a product tile holds both halves of every pair it covers
+        self.gate_up = stack([torch.stack((tensors[g], tensors[u]), dim=1).reshape(2 * self.intermediate, self.hidden)
+                              for g, u, _ in experts])                                                 # [E, 2 ff, d]
         self.down = stack([tensors[dn] for _, _, dn in experts])                                       # [E, d, ff]
         self.runtime = runtime
+        self.tensor_cores = runtime.dtype == "bfloat16" and self.hidden % 8 == 0 and self.intermediate % 8 == 0
+
+    def tile_rows(self, n_tokens: int) -> int:
+        """Height of a token tile of the grouped tensor-core products: about the rows an expert gets on average."""
+        per = -(-n_tokens * self.top // self.n_experts)
+        return 256 if per >= 1024 else 128 if per > 64 else max(16, -(-per // 16) * 16)
 
     def forward(self, x: torch.Tensor, ctx, residual: torch.Tensor, accumulate: bool = True) -> None:
         rt = self.runtime
         logits = ops.gemm_simt(x, self.router, out_dtype=torch.float32)
         chosen, weight = ops.moe_route(logits, self.top, self.n_groups, self.group_keep, self.renormalize)
-        plan = ops.moe_sort(chosen, self.n_experts)
-        h = ops.moe_gemm(0, x, self.gate_up, plan, rt.act_dtype)
-        parts = ops.moe_gemm(1, h, self.down, plan, torch.float32)
+        parts = row_of = None
+        if self.tensor_cores:
+            plan = ops.moe_sort_padded(chosen, self.n_experts, self.tile_rows(x.shape[0]))
+            xp = ops.moe_gather(x, plan)
+            E, ff, d = self.n_experts, self.intermediate, self.hidden
+            h = ops.gemm_tcgen05_grouped(xp, self.gate_up.view(E * 2 * ff, d), plan, torch.bfloat16, swiglu=True, status=rt.status)
+            if h is not None:
+                parts = ops.gemm_tcgen05_grouped(h, self.down.view(E * d, ff), plan, torch.float32, status=rt.status)
+                row_of = plan.row_of
+        if parts is None:
+            plan = ops.moe_sort(chosen, self.n_experts)
+            h = ops.moe_gemm(0, x, self.gate_up, plan, rt.act_dtype)
+            parts = ops.moe_gemm(1, h, self.down, plan, torch.float32)
+            row_of = None
         if accumulate:
-            ops.add_(residual, ops.moe_combine(parts, weight))
+            ops.add_(residual, ops.moe_combine(parts, weight, row_of=row_of))
         else:
-            ops.moe_combine(parts, weight, out=residual)
+            ops.moe_combine(parts, weight, out=residual, row_of=row_of)
 
 
 register_feed_forward("moe", MoEFeedForward)

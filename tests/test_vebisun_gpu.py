@@ -309,6 +309,37 @@ def test_convolution_rotation_append_kernel(dtype, taps, rot, pairing, hd, hdv):
         assert rel_err(kk.numpy(), k.numpy()) < tol and rel_err(vv.numpy(), v.numpy()) < tol
 
 
+@pytest.mark.parametrize("T,E,top,ff,d", [(5, 16, 2, 96, 256), (700, 4, 2, 200, 128), (2500, 2, 1, 64, 64), (200, 64, 1, 48, 64),
+                                          (64, 8, 8, 72, 200)])
+def test_mixture_of_experts_on_the_grouped_tensor_core_product(monkeypatch, T, E, top, ff, d):
+    """Tile heights of 16, 128 and 256 rows; experts that get no token; widths that are no multiple of the 128-row
+    weight tile or the 64-wide K block.  The CUDA-core product must not run."""
+    from ithaca_b200.config.spec import PartSpec
+    from ithaca_b200.csrc import ops
+    from ithaca_b200.parts import FEED_FORWARDS, Runtime
+    g = torch.Generator().manual_seed(T + E)
+    spec = PartSpec("moe", {"hidden_size": d, "intermediate_size": ff, "n_experts": E, "top": top},
+                    {"router": "router", "gate": "e{e}.gate", "up": "e{e}.up", "down": "e{e}.down"})
+    t = {"router": (torch.randn(E, d, generator=g) * 0.4).bfloat16()}
+    for e in range(E):
+        t[f"e{e}.gate"] = (torch.randn(ff, d, generator=g) * 0.2).bfloat16()
+        t[f"e{e}.up"] = (torch.randn(ff, d, generator=g) * 0.2).bfloat16()
+        t[f"e{e}.down"] = (torch.randn(d, ff, generator=g) * 0.2).bfloat16()
+    rt = Runtime(dtype="bfloat16", device="cuda:0")
+    part = FEED_FORWARDS.get("moe")(spec, t, rt)
+    assert part.tensor_cores
+
+    def never(*a, **k):
+        raise AssertionError("the CUDA-core grouped product ran")
+    monkeypatch.setattr(ops, "moe_gemm", never)
+    x = torch.randn(T, d, generator=g).bfloat16()
+    want = P.moe_ff(x.double(), {"router": {"experts": E, "top": top}}, t, "")
+    out = torch.full((T, d), 7.0, device="cuda")
+    part.forward(x.cuda(), None, out, accumulate=False)
+    assert int(rt.status.item()) == 0
+    assert rel_err(out.cpu().numpy(), want.numpy()) < 2e-2
+
+
 # ------------------------------------------------------------------------------------------ whole models
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 @pytest.mark.parametrize("name", ["A", "B"])
