@@ -3,6 +3,9 @@
     python bench.py [--gpus 1] [--steps K] [--warmup W] [--batch 8] [--layers N] [--impl reference]
     python bench.py --only decode|prefill|attention|products   one part alone (small cases for profiling)
     python bench.py --only marginal [--batch B]                 what each kernel family costs inside the replayed decode step
+    python bench.py --only vebisun [--batch B]                  the Vebisun decoder at a few sizes beside a Llama of equal width,
+                                                                heads and active feed-forward size: prefill and decode tok/s and
+                                                                every kernel's fraction of the device's peaks
     python bench.py --config 1b-unequal|13b-long                the other two workloads alone, through Engine.generate
 
 Prints ONE JSON line.  ``value`` is decoded tokens per second at the given batch with every
@@ -487,6 +490,82 @@ def marginal_run(eng, cfg, batch, vocab, context, steps=30):
     return out
 
 
+# Sizes that resemble real layers: (name, width, heads, kv heads, head size, experts, chosen, expert width, groups, kept,
+# window, layers, (loop start, stop, times)).
+VEBISUN_SIZES = [
+    ("2048 wide, 32 experts of 1024, 4 chosen", 2048, 16, 4, 128, 32, 4, 1024, 4, 2, 1024, 4, (1, 3, 2)),
+    ("4096 wide, 16 experts of 3584, 2 chosen", 4096, 32, 8, 128, 16, 2, 3584, 2, 1, 2048, 3, (0, 1, 2)),
+]
+
+
+def vebisun_pair(size, vocab=32000):
+    """The Vebisun configuration of a size and the Llama next to it: the same width, heads and head size, as many layers
+    as the Vebisun model has layer runs, a feed-forward as wide as the experts a token uses together, the same window."""
+    _, d, nh, nkv, hd, E, top, ff, ng, keep, window, layers, loop = size
+    mixer = {"heads": nh, "kv_heads": nkv, "dim": hd, "vdim": hd, "conv": 4, "scale": hd ** -0.5, "softcap": 50.0,
+             "mask": {"size": window},
+             "rot": {"base": 500000.0, "dims": hd // 2, "scaling": {"factor": 8.0, "low": 1.0, "high": 4.0, "original": 8192}}}
+    mlp = {"kind": "moe", "expert": {"ff": ff}, "router": {"experts": E, "top": top, "groups": {"count": ng, "keep": keep}}}
+    veb = {"architecture": "Vebisun", "vocab": vocab, "width": d, "embedding": {"scale": 1.0}, "residual_mult": 0.5,
+           "norm": {"eps": 1e-6}, "layers": [{"type": "attention", "mixer": mixer, "mlp": mlp} for _ in range(layers)],
+           "loop": {"start": loop[0], "stop": loop[1], "times": loop[2]}}
+    runs = layers + (loop[1] - loop[0]) * (loop[2] - 1)
+    llama = {"architectures": ["LlamaForCausalLM"], "hidden_size": d, "num_hidden_layers": runs, "num_attention_heads": nh,
+             "num_key_value_heads": nkv, "head_dim": hd, "intermediate_size": top * ff, "vocab_size": vocab, "rope_theta": 500000.0,
+             "rope_scaling": None, "rms_norm_eps": 1e-6, "max_position_embeddings": 131072, "tie_word_embeddings": False,
+             "torch_dtype": "bfloat16", "sliding_window": window, "use_sliding_window": True}
+    return veb, llama, runs
+
+
+def vebisun_run(pk, batch, steps, warmup, context=2048, prompt=4096):
+    """Per size and model: tok/s of one prompt of ``prompt`` tokens, tok/s of graph-replayed decode steps at ``batch``
+    sequences of ``context`` positions, and per kernel of a prompt step and of a decode step its time and its better
+    fraction of the two peaks (bytes over the copy bandwidth, operations over the bfloat16 product rate)."""
+    import gc
+    import numpy as np
+    import torch
+    from ithaca_b200 import Engine
+    out = []
+    for size in VEBISUN_SIZES:
+        veb, llama, runs = vebisun_pair(size)
+        row = {"size": size[0], "layer_runs": runs, "prompt": prompt, "decode_batch": batch, "decode_context": context}
+        for name, cfg in (("vebisun", veb), ("llama", llama)):
+            vocab = cfg.get("vocab", cfg.get("vocab_size"))
+            eng = Engine.from_random(cfg, seed=0, dtype="bfloat16", max_tokens=(batch + 1) * (max(context, prompt) + 128),
+                                     ctx=max(context, prompt) + 128, max_step_tokens=max(16384, prompt))
+            pre_ms = prefill_run(eng, prompt, vocab, reps=3)
+            dec = decode_run(eng, batch, steps, warmup, vocab, context)
+            rng = np.random.default_rng(3)
+
+            def kernels(slots, tokens):
+                _, rows = eng.profile_step(slots, tokens)
+                return [{"kernel": r["kernel"], "calls": r["calls"], "us": round(r["us"], 1),
+                         "of_peak": round(max(r["bytes"] / (r["us"] / 1e6) / 1e9 / pk["hbm_gbs"],
+                                              r["flops"] / (r["us"] / 1e6) / 1e12 / pk["bf16_tflops"]), 3) if r["us"] > 0 else None}
+                        for r in rows]
+            s = eng.alloc_slot()
+            eng.step([s], [rng.integers(0, vocab, size=prompt).tolist()], None)           # warm: modules loaded, buffers made
+            eng.free_slot(s)
+            s = eng.alloc_slot()
+            pre_rows = kernels([s], [rng.integers(0, vocab, size=prompt).tolist()])
+            eng.free_slot(s)
+            slots = [eng.alloc_slot() for _ in range(batch)]
+            fill_cache(eng, slots, context - 2, vocab, seed=7)
+            eng.step(slots, [[1] for _ in slots], None)
+            dec_rows = kernels(slots, [[2] for _ in slots])
+            for s in slots:
+                eng.free_slot(s)
+            row[name] = {"prefill_tok_s": round(prompt / (pre_ms / 1e3), 1), "prefill_ms": round(pre_ms, 3),
+                         "decode_tok_s": round(dec["tok_s"], 1), "decode_ms_per_step": round(dec["ms_per_step"], 4),
+                         "decode_launches": dec["launches_per_step"], "weight_gb": round(eng.model.weight_bytes() / 1e9, 3),
+                         "prefill_kernels": pre_rows, "decode_kernels": dec_rows}
+            del eng
+            gc.collect()
+            torch.cuda.empty_cache()
+        out.append(row)
+    return out
+
+
 def attempt(run, eng=None):
     """One part of the line: run it, once more if it raises, and if it raises again say so in its place.  The other
     parts of the line stand on their own measurements and are printed all the same."""
@@ -530,7 +609,7 @@ def main():
                     help="with --only decode / prefill: another context length (decode) or prompt length (prefill) than the default run's")
     ap.add_argument("--config", default=None, choices=["1b-unequal", "13b-long"],
                     help="run one of the other workloads alone and print its figures")
-    ap.add_argument("--only", default="all", choices=["all", "decode", "prefill", "attention", "products", "marginal", "issue-rate"],
+    ap.add_argument("--only", default="all", choices=["all", "decode", "prefill", "attention", "products", "marginal", "issue-rate", "vebisun"],
                     help="run one part only and print its figures (for profiling a small case)")
     args = ap.parse_args()
 
@@ -554,6 +633,9 @@ def main():
         return 0
     shape_name, shape_cfg = SHAPES[args.shape]
     cfg = dict(shape_cfg)
+    if args.only == "vebisun":
+        print(json.dumps({"only": "vebisun", "peaks": pk, "sizes": vebisun_run(pk, args.batch, min(args.steps, 64), args.warmup)}))
+        return 0
     if args.only == "issue-rate":
         # what the thread that issues tensor-core products costs: cycles per instruction, one or two issuing threads
         from ithaca_b200.csrc import ops

@@ -1,7 +1,8 @@
 // Mixture of experts: routing, the grouping of (token, choice) pairs by expert, the experts' products
 // over those groups, and the weighted sum of a token's choices.
 //
-//   route     scores = softmax(router logits) over all experts (float).  Experts form `n_groups` equal groups of
+//   router    the router's logits z = Wr x (float products, float sums) and the routing below, in one kernel.
+//   route     (the routing alone, from ready-made logits) scores = softmax(router logits) over all experts (float).  Experts form `n_groups` equal groups of
 //             neighbours; a group counts by its best score, only experts of the `keep` best groups can be chosen
 //             (n_groups <= 1: all can), and the `top` best of them are.  The weights are the chosen experts' scores as
 //             they are, or divided by their sum (renorm).  Equal scores: the lower index wins.
@@ -28,26 +29,15 @@ namespace {
 constexpr int MOE_BM = 64, MOE_BN = 64, MOE_BK = 16, MOE_TM = 4, MOE_TN = 4;
 
 // ------------------------------------------------------------------------------------------ route
-// One warp per token.  smem: scores [E] then group bests [n_groups] per warp.
-__global__ void __launch_bounds__(128)
-moe_route_kernel(const float* __restrict__ logits, int* __restrict__ chosen, float* __restrict__ weight, int T, int E,
-                 int top, int n_groups, int keep, int renorm) {
-    ik_pdl_wait();
-    IK_AFTER_WAIT(logits);
-    ik_pdl_launch_dependents();
-    extern __shared__ float sm[];
-    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int t = blockIdx.x * 4 + warp;
-    if (t >= T) return;
-    const int ng = n_groups > 1 ? n_groups : 0;
-    float* sc = sm + (size_t)warp * (E + ng);
-    float* gb = sc + E;
-    const float* z = logits + (size_t)t * E;
+// One warp routes one token.  sc [E]: the token's router logits on entry (any memory the warp may write), its scores
+// with the taken ones marked on exit; gb [n_groups]: scratch.
+__device__ __forceinline__ void route_token(float* sc, float* gb, int lane, int* __restrict__ chosen, float* __restrict__ weight,
+                                            int E, int top, int ng, int keep, int renorm) {
     float m = -INFINITY;
-    for (int e = lane; e < E; e += 32) m = fmaxf(m, z[e]);
+    for (int e = lane; e < E; e += 32) m = fmaxf(m, sc[e]);
     for (int o = 16; o > 0; o >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, o));
     float sum = 0.f;
-    for (int e = lane; e < E; e += 32) { const float p = expf(z[e] - m); sc[e] = p; sum += p; }
+    for (int e = lane; e < E; e += 32) { const float p = expf(sc[e] - m); sc[e] = p; sum += p; }
     for (int o = 16; o > 0; o >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, o);
     const float inv = 1.0f / sum;
     for (int e = lane; e < E; e += 32) sc[e] *= inv;
@@ -77,7 +67,7 @@ moe_route_kernel(const float* __restrict__ logits, int* __restrict__ chosen, flo
             if (lane == 0) gb[g] = -1.f;
             __syncwarp();
         }
-        for (int e = lane; e < E; e += 32) if (gb[e / per] != -1.f) sc[e] = -(sc[e] + 2.f);     // struck out, score kept: -(s + 2) <= -2
+        for (int e = lane; e < E; e += 32) if (gb[e / per] != -1.f) sc[e] = -(sc[e] + 2.f);     // struck out: -(s + 2) <= -2
         __syncwarp();
     }
     float wsum = 0.f;
@@ -86,10 +76,78 @@ moe_route_kernel(const float* __restrict__ logits, int* __restrict__ chosen, flo
         const float s = sc[e];
         wsum += s;
         __syncwarp();
-        if (lane == 0) { chosen[(size_t)t * top + k] = e; weight[(size_t)t * top + k] = s; sc[e] = -1.f; }
+        if (lane == 0) { chosen[k] = e; weight[k] = s; sc[e] = -1.f; }
         __syncwarp();
     }
-    if (renorm && lane == 0) for (int k = 0; k < top; k++) weight[(size_t)t * top + k] /= wsum;
+    if (renorm && lane == 0) for (int k = 0; k < top; k++) weight[k] /= wsum;
+}
+
+// From ready-made logits: one warp per token.  smem: scores [E] then group bests [n_groups] per warp.
+__global__ void __launch_bounds__(128)
+moe_route_kernel(const float* __restrict__ logits, int* __restrict__ chosen, float* __restrict__ weight, int T, int E,
+                 int top, int n_groups, int keep, int renorm) {
+    ik_pdl_wait();
+    IK_AFTER_WAIT(logits);
+    ik_pdl_launch_dependents();
+    extern __shared__ float sm[];
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int t = blockIdx.x * 4 + warp;
+    if (t >= T) return;
+    const int ng = n_groups > 1 ? n_groups : 0;
+    float* sc = sm + (size_t)warp * (E + ng);
+    for (int e = lane; e < E; e += 32) sc[e] = logits[(size_t)t * E + e];
+    __syncwarp();
+    route_token(sc, sc + E, lane, chosen + (size_t)t * top, weight + (size_t)t * top, E, top, ng, keep, renorm);
+}
+
+// The router's product and the routing in one kernel.  A block takes TOK tokens: their activations go to shared memory
+// as floats; warp w forms the logits of experts w, w + 8, ...: its lanes stride over K (a weight row is read once per block,
+// 128 bytes per warp and load), each lane keeps one partial sum per token, added over k = lane, lane + 32, ... in
+// ascending order and then across the lanes by a fixed tree, so a logit depends on its token and expert alone.  Then warp
+// w routes token w.  Everything in float.  smem: x [TOK][K], logits [TOK][E + n_groups].
+template <int TOK, typename TX>
+__global__ void __launch_bounds__(256)
+moe_router_kernel(const TX* __restrict__ x, const float* __restrict__ wr, int* __restrict__ chosen, float* __restrict__ weight,
+                  int T, int K, int E, int top, int n_groups, int keep, int renorm, int ldx) {
+    ik_pdl_wait();
+    IK_AFTER_WAIT(x);
+    ik_pdl_launch_dependents();
+    extern __shared__ float sm[];
+    const int ng = n_groups > 1 ? n_groups : 0;
+    float* xs = sm;                                   // [TOK][K]
+    float* lg = sm + (size_t)TOK * K;                 // [TOK][E + ng]
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int t0 = blockIdx.x * TOK;
+    for (int idx = threadIdx.x; idx < TOK * K; idx += 256) {
+        const int i = idx / K, k = idx - i * K;
+        xs[idx] = t0 + i < T ? ik_ld(x, (size_t)(t0 + i) * ldx + k) : 0.f;
+    }
+    __syncthreads();
+    for (int e = warp; e < E; e += 8) {
+        const float* w = wr + (size_t)e * K;
+        float acc[TOK];
+        #pragma unroll
+        for (int i = 0; i < TOK; i++) acc[i] = 0.f;
+        #pragma unroll 4
+        for (int k = lane; k < K; k += 32) {
+            const float wv = __ldg(w + k);
+            #pragma unroll
+            for (int i = 0; i < TOK; i++) acc[i] = fmaf(xs[i * K + k], wv, acc[i]);
+        }
+        #pragma unroll
+        for (int i = 0; i < TOK; i++) {
+            float v = acc[i];
+            for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+            if (lane == 0) lg[i * (E + ng) + e] = v;
+        }
+    }
+    __syncthreads();
+    for (int i = warp; i < TOK; i += 8) {
+        const int t = t0 + i;
+        if (t >= T) continue;
+        float* sc = lg + (size_t)i * (E + ng);
+        route_token(sc, sc + E, lane, chosen + (size_t)t * top, weight + (size_t)t * top, E, top, ng, keep, renorm);
+    }
 }
 
 // ------------------------------------------------------------------------------------------ sort
@@ -309,6 +367,34 @@ IK_EXPORT int ik_moe_route(const float* logits, int* chosen, float* weight, int 
     const size_t smem = 4 * (size_t)(E + (n_groups > 1 ? n_groups : 0)) * sizeof(float);
     if (smem > 48 * 1024) return IK_UNSUPPORTED;
     IK_RETURN_IF_ERROR(ik_launch(moe_route_kernel, (T + 3) / 4, 128, smem, stream, logits, chosen, weight, T, E, top, n_groups, keep, renorm));
+    IK_LAUNCH_STATUS();
+}
+
+// x [T, K] (float or bfloat16, rows ldx apart), wr [E, K] float -> chosen, weight [T, top]
+IK_EXPORT int ik_moe_router(const void* x, int x_dtype, const float* wr, int* chosen, float* weight, int T, int K, int E, int top,
+                            int n_groups, int keep, int renorm, int ldx, cudaStream_t stream) {
+    if (T < 0 || E <= 0 || K <= 0 || top <= 0 || top > E || ldx < K) return IK_BAD_ARGUMENT;
+    if (n_groups > 1 && (E % n_groups || keep <= 0 || keep > n_groups || top > keep * (E / n_groups))) return IK_BAD_ARGUMENT;
+    if (T == 0) return IK_OK;
+    const int ng = n_groups > 1 ? n_groups : 0;
+    // few tokens (decode): a block per token, so that the step's tokens spread over the SMs; else eight tokens a block
+    const int tok = T <= 64 ? 1 : 8;
+    const size_t smem = ((size_t)tok * K + (size_t)tok * (E + ng)) * sizeof(float);
+    if (smem > 200 * 1024) return IK_UNSUPPORTED;
+#define IK_ROUTER(TOK, TX)                                                                                                 \
+    {                                                                                                                      \
+        auto kern = moe_router_kernel<TOK, TX>;                                                                            \
+        if (smem > 48 * 1024) {                                                                                            \
+            cudaError_t e0 = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);           \
+            if (e0 != cudaSuccess) return (int)e0;                                                                         \
+        }                                                                                                                  \
+        IK_RETURN_IF_ERROR(ik_launch(kern, (T + TOK - 1) / TOK, 256, smem, stream, (const TX*)x, wr, chosen, weight, T, K, E, top, \
+                                     n_groups, keep, renorm, ldx));                                                        \
+    }
+    if (x_dtype == IK_F32) { if (tok == 1) IK_ROUTER(1, float) else IK_ROUTER(8, float) }
+    else if (x_dtype == IK_BF16) { if (tok == 1) IK_ROUTER(1, __nv_bfloat16) else IK_ROUTER(8, __nv_bfloat16) }
+    else return IK_BAD_ARGUMENT;
+#undef IK_ROUTER
     IK_LAUNCH_STATUS();
 }
 

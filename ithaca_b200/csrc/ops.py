@@ -91,6 +91,7 @@ _SIGNATURES = {
                             _i, _i, _i, _i, _i, _vp, _vp],
     "ik_moe_tile_rows": [],
     "ik_moe_route": [_vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _vp],
+    "ik_moe_router": [_vp, _i, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _i, _i, _vp],
     "ik_moe_sort": [_vp, _vp, _vp, _vp, _vp, _i, _i, _i, _vp],
     "ik_moe_gemm": [_i, _vp, _i, _vp, _i, _vp, _i, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _vp],
     "ik_moe_combine": [_vp, _vp, _vp, _vp, _i, _i, _i, _vp],
@@ -624,7 +625,7 @@ def conv_rope_append(qkv: torch.Tensor, conv_w: Optional[torch.Tensor], ring: Op
                      v_pages: torch.Tensor, token_seq: torch.Tensor, token_pos: torch.Tensor, table: torch.Tensor,
                      inv_freq: Optional[torch.Tensor], n_heads: int, n_kv_heads: int, rotary_dim: int, pairing: int,
                      write_cache: bool, status: Optional[torch.Tensor]) -> None:
-    """Short causal convolution over time on the projected q, k, v (``conv_w`` [channels, taps]; None = no
+    """Short causal convolution over time on the projected q, k, v (``conv_w`` [taps, channels], tap-major; None = no
     convolution), rotary encoding of q and k, append of k and v to the pages.  ``ring`` [max_slots, taps, channels]
     holds each sequence's last projected values and is brought up to date."""
     _need(qkv, "qkv", torch.float32)
@@ -638,9 +639,9 @@ def conv_rope_append(qkv: torch.Tensor, conv_w: Optional[torch.Tensor], ring: Op
     taps = 0
     if conv_w is not None:
         _need(conv_w, "conv_w", torch.float32)
-        taps = conv_w.shape[1]
-        if conv_w.shape[0] != ctot:
-            raise KernelError("conv_rope_append: one row of taps per channel is needed")
+        taps = conv_w.shape[0]
+        if conv_w.shape[1] != ctot:
+            raise KernelError("conv_rope_append: one row of channels per tap is needed")
         if taps > 1:
             _need(ring, "ring", torch.float32)
             if tuple(ring.shape[1:]) != (taps, ctot):
@@ -666,6 +667,27 @@ def moe_route(logits: torch.Tensor, top: int, n_groups: int = 0, keep: int = 0, 
     _work(f"moe_route {T}x{E}", _nbytes(logits, chosen, weight))
     _check(lib().ik_moe_route(_ptr(logits), _ptr(chosen), _ptr(weight), T, E, top, n_groups, keep, 1 if renorm else 0, _stream()),
            "moe_route")
+    return chosen, weight
+
+
+def moe_router(x: torch.Tensor, router: torch.Tensor, top: int, n_groups: int = 0, keep: int = 0, renorm: bool = False):
+    """The router's logits ``x router^T`` (float products and sums, whatever type ``x`` has) and the routing of
+    ``moe_route``, in one kernel.  Returns (chosen int32 [T, top], weights float [T, top]), or None when the kernel does
+    not take these sizes (the caller forms the logits with a product and routes them)."""
+    _need(x, "x", contiguous=False)
+    _need(router, "router", torch.float32)
+    T, K = x.shape
+    E = router.shape[0]
+    if router.shape[1] != K or x.stride(1) != 1:
+        raise KernelError("moe_router: the sizes do not fit together")
+    chosen = torch.empty((T, top), dtype=torch.int32, device=x.device)
+    weight = torch.empty((T, top), dtype=torch.float32, device=x.device)
+    _work(f"moe_router {T}x{E}x{K}", T * K * x.element_size() + E * K * 4 + 8 * T * top, 2 * T * E * K)
+    st = lib().ik_moe_router(_ptr(x), _code(x), _ptr(router), _ptr(chosen), _ptr(weight), T, K, E, top, n_groups, keep,
+                             1 if renorm else 0, x.stride(0), _stream())
+    if st == -2:
+        return None
+    _check(st, "moe_router")
     return chosen, weight
 
 

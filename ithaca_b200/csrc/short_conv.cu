@@ -1,7 +1,7 @@
 // A short causal convolution over time on every channel of the projected q, k and v, fused with the rotary
 // encoding of q and k and the append of k and v to the paged cache.
 //
-//   y[p, c] = sum_{j < taps} w[c, j] * u[p - taps + 1 + j, c],   u = 0 before the sequence's start,
+//   y[p, c] = sum_{j < taps} w[j, c] * u[p - taps + 1 + j, c],   u = 0 before the sequence's start (w tap-major: [taps, channels]),
 //
 // u being the projections [T, nh*hd | nkv*hd | nkv*hdv] of the step's tokens (float).  Values of u at
 // positions before the step's first token come from the sequence's ring: ring[slot][p % taps][c] holds u[p, c]
@@ -69,7 +69,7 @@ conv_rope_append_kernel(ConvArgs a, TQ* __restrict__ q_out, TC* __restrict__ k_p
             const int back = taps - 1 - j, p = pos - back;
             if (p < 0) continue;
             const float u = p >= pos_start ? *(here - (size_t)back * ctot) : ring[(size_t)(p % taps) * ctot + c];
-            acc = fmaf(a.conv_w[(size_t)c * taps + j], u, acc);
+            acc = fmaf(a.conv_w[(size_t)j * ctot + c], u, acc);
         }
         return acc;
     };
@@ -100,6 +100,76 @@ conv_rope_append_kernel(ConvArgs a, TQ* __restrict__ q_out, TC* __restrict__ k_p
             TC* vdst = v_pages + (page_row + (size_t)g * a.page_size) * hdv;
             for (int i = threadIdx.x; i < hdv; i += blockDim.x) ik_st(vdst, i, conv_at(c0 + i));
         }
+    }
+}
+
+// The same, four neighbouring channels a thread with 16-byte loads and stores: for neighbouring rotary pairs (pairing 1) or
+// no rotation, and head sizes, rotated width and channel count that are multiples of 4.  A block takes 1024 channels of
+// one token.
+template <typename TQ, typename TC>
+__global__ void __launch_bounds__(256)
+conv_rope_append_vec_kernel(ConvArgs a, TQ* __restrict__ q_out, TC* __restrict__ k_pages, TC* __restrict__ v_pages, int* status) {
+    extern __shared__ __align__(16) float cs[];    // [rot/2] cos, then [rot/2] sin of this token's angles
+    ik_pdl_wait();
+    IK_AFTER_WAIT(a.qkv);
+    IK_AFTER_WAIT(a.ring);
+    IK_AFTER_WAIT(a.slots);
+    IK_AFTER_WAIT(a.cu_seqlens);
+    IK_AFTER_WAIT(a.token_seq);
+    IK_AFTER_WAIT(a.token_pos);
+    IK_AFTER_WAIT(a.table);
+    ik_pdl_launch_dependents();
+    const int t = blockIdx.x, half = a.rot / 2;
+    const int nh = a.nh, nkv = a.nkv, hd = a.hd, hdv = a.hdv, taps = a.taps, ctot = a.ctot;
+    const int pos = a.token_pos[t], seq = a.token_seq[t];
+    const int pos_start = pos - (t - a.cu_seqlens[seq]);
+    const int c_lo = blockIdx.y * 1024;
+    const int q_end = nh * hd, k_end = (nh + nkv) * hd;
+    if (c_lo < k_end) {
+        for (int i = threadIdx.x; i < half; i += 256) {
+            const float ang = __fmul_rn((float)pos, a.inv_freq[i]);
+            cs[i] = cosf(ang);
+            cs[half + i] = sinf(ang);
+        }
+    }
+    __syncthreads();
+    const int c = c_lo + 4 * threadIdx.x;
+    if (c >= ctot) return;
+    const float* ring = a.ring ? a.ring + (size_t)a.slots[seq] * taps * ctot : nullptr;
+    const float* here = a.qkv + (size_t)t * ctot + c;
+    float4 y;
+    if (taps <= 0) {
+        y = *reinterpret_cast<const float4*>(here);
+    } else {
+        y = make_float4(0.f, 0.f, 0.f, 0.f);
+        for (int j = 0; j < taps; j++) {
+            const int back = taps - 1 - j, p = pos - back;
+            if (p < 0) continue;
+            const float4 u = *reinterpret_cast<const float4*>(p >= pos_start ? here - (size_t)back * ctot : ring + (size_t)(p % taps) * ctot + c);
+            const float4 w = *reinterpret_cast<const float4*>(a.conv_w + (size_t)j * ctot + c);
+            y.x = fmaf(w.x, u.x, y.x); y.y = fmaf(w.y, u.y, y.y); y.z = fmaf(w.z, u.z, y.z); y.w = fmaf(w.w, u.w, y.w);
+        }
+    }
+    if (c < k_end) {
+        const int i = c % hd;                                   // q and k heads have the same size
+        if (i < a.rot) {
+            const float c0 = cs[i / 2], s0 = cs[half + i / 2], c1 = cs[i / 2 + 1], s1 = cs[half + i / 2 + 1];
+            const float4 r = make_float4(__fsub_rn(__fmul_rn(y.x, c0), __fmul_rn(y.y, s0)), __fadd_rn(__fmul_rn(y.y, c0), __fmul_rn(y.x, s0)),
+                                         __fsub_rn(__fmul_rn(y.z, c1), __fmul_rn(y.w, s1)), __fadd_rn(__fmul_rn(y.w, c1), __fmul_rn(y.z, s1)));
+            y = r;
+        }
+        if (c < q_end) { ik_st4(q_out, (size_t)t * q_end + c, y); return; }
+    }
+    if (!a.write_cache) return;
+    const int page = a.table[(size_t)seq * a.table_stride + pos / a.page_size];
+    if (page < 0 || page >= a.n_pages) { ik_set_status(status, IK_STATUS_WRITE_NO_PAGE); return; }
+    const size_t page_row = (size_t)page * nkv * a.page_size + (pos % a.page_size);
+    if (c < k_end) {
+        const int g = (c - q_end) / hd, i = (c - q_end) % hd;
+        ik_st4(k_pages, (page_row + (size_t)g * a.page_size) * hd + i, y);
+    } else {
+        const int g = (c - k_end) / hdv, i = (c - k_end) % hdv;
+        ik_st4(v_pages, (page_row + (size_t)g * a.page_size) * hdv + i, y);
     }
 }
 
@@ -139,11 +209,17 @@ IK_EXPORT int ik_conv_rope_append(const float* qkv, const float* conv_w, float* 
     dim3 grid(T, (nh + 2 * nkv + hpb - 1) / hpb);
     const dim3 threads(32, 8);
     const size_t smem = (size_t)rot * sizeof(float);
-#define IK_CONV(TQ, TC) IK_RETURN_IF_ERROR(ik_launch(conv_rope_append_kernel<TQ, TC>, grid, threads, smem, stream, a, (TQ*)q_out, (TC*)k_pages, (TC*)v_pages, status))
-    if (q_dtype == IK_F32 && cache_dtype == IK_F32) IK_CONV(float, float);
-    else if (q_dtype == IK_BF16 && cache_dtype == IK_BF16) IK_CONV(__nv_bfloat16, __nv_bfloat16);
-    else if (q_dtype == IK_F32 && cache_dtype == IK_BF16) IK_CONV(float, __nv_bfloat16);
-    else if (q_dtype == IK_BF16 && cache_dtype == IK_F32) IK_CONV(__nv_bfloat16, float);
+    const bool vec = (rot == 0 || pairing == 1) && hd % 4 == 0 && hdv % 4 == 0 && rot % 4 == 0 && ((uintptr_t)qkv % 16) == 0 &&
+                     ((uintptr_t)conv_w % 16) == 0 && ((uintptr_t)ring % 16) == 0 && ((uintptr_t)q_out % 16) == 0 &&
+                     ((uintptr_t)k_pages % 16) == 0 && ((uintptr_t)v_pages % 16) == 0;
+    const dim3 vgrid(T, (a.ctot + 1023) / 1024);
+#define IK_CONV(TQ, TC)                                                                                                                \
+    if (vec) IK_RETURN_IF_ERROR(ik_launch(conv_rope_append_vec_kernel<TQ, TC>, vgrid, 256, smem, stream, a, (TQ*)q_out, (TC*)k_pages, (TC*)v_pages, status)); \
+    else IK_RETURN_IF_ERROR(ik_launch(conv_rope_append_kernel<TQ, TC>, grid, threads, smem, stream, a, (TQ*)q_out, (TC*)k_pages, (TC*)v_pages, status))
+    if (q_dtype == IK_F32 && cache_dtype == IK_F32) { IK_CONV(float, float); }
+    else if (q_dtype == IK_BF16 && cache_dtype == IK_BF16) { IK_CONV(__nv_bfloat16, __nv_bfloat16); }
+    else if (q_dtype == IK_F32 && cache_dtype == IK_BF16) { IK_CONV(float, __nv_bfloat16); }
+    else if (q_dtype == IK_BF16 && cache_dtype == IK_F32) { IK_CONV(__nv_bfloat16, float); }
     else return IK_BAD_ARGUMENT;
 #undef IK_CONV
     if (taps > 1 && write_cache && n_seqs > 0) {

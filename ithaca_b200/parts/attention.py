@@ -95,7 +95,7 @@ class Attention:
         self.channels = (self.n_heads + self.n_kv_heads) * self.head_dim + self.n_kv_heads * self.v_head_dim
         if self.conv_taps:
             cw = torch.cat([tensors[w[r]].to(torch.float32) for r in ("q_conv", "k_conv", "v_conv")], dim=0)
-            self.conv_weight = cw.to(runtime.device).contiguous()
+            self.conv_weight = cw.to(runtime.device).t().contiguous()              # tap-major [taps, channels]: a tap's weights of neighbouring channels lie together
         # the plain path (projections, then convolution, rotation and append in one kernel) serves every option
         self.plain_append = bool(self.conv_taps) or self.v_head_dim != self.head_dim
 

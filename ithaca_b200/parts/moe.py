@@ -6,7 +6,7 @@ score, and only experts of the ``group_keep`` best groups can be chosen.  The ``
 them are; their weights are their scores (``renormalize``: divided by their sum).  An expert is
 y = Wd (silu(Wg x) * (Wu x)); the layer's output is the weighted sum of the chosen experts'.
 
-On the device: one kernel picks experts and weights per token; a counting sort groups the
+On the device: one kernel forms the router's logits and picks experts and weights per token; a counting sort groups the
 (token, choice) pairs by expert; two grouped products run every expert over its rows (the first
 with silu(g) * u as its epilogue, so the [rows, 2 ff] intermediate is never written); a last kernel
 adds a token's choices in the order they were chosen.  Nothing is read back by the host: grids are
@@ -92,8 +92,11 @@ class MoEFeedForward:
 
     def forward(self, x: torch.Tensor, ctx, residual: torch.Tensor, accumulate: bool = True) -> None:
         rt = self.runtime
-        logits = ops.gemm_simt(x, self.router, out_dtype=torch.float32)
-        chosen, weight = ops.moe_route(logits, self.top, self.n_groups, self.group_keep, self.renormalize)
+        routed = ops.moe_router(x, self.router, self.top, self.n_groups, self.group_keep, self.renormalize)
+        if routed is None:                                   # sizes beyond the fused kernel's shared memory
+            logits = ops.gemm_simt(x, self.router, out_dtype=torch.float32)
+            routed = ops.moe_route(logits, self.top, self.n_groups, self.group_keep, self.renormalize)
+        chosen, weight = routed
         parts = row_of = None
         if self.tensor_cores:
             plan = ops.moe_sort_padded(chosen, self.n_experts, self.tile_rows(x.shape[0]))

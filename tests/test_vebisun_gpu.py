@@ -257,7 +257,8 @@ def test_tensor_core_attention_with_capped_scores(nh, nkv, hd, kind, cap, window
 
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
-@pytest.mark.parametrize("taps,rot,pairing,hd,hdv", [(3, 8, 1, 16, 24), (4, 16, 0, 16, 16), (1, 0, 1, 8, 8), (2, 32, 1, 32, 8), (0, 8, 1, 16, 24)])
+@pytest.mark.parametrize("taps,rot,pairing,hd,hdv", [(3, 8, 1, 16, 24), (4, 16, 0, 16, 16), (1, 0, 1, 8, 8), (2, 32, 1, 32, 8), (0, 8, 1, 16, 24),
+                                                      (3, 6, 1, 10, 6), (4, 12, 1, 12, 12), (2, 0, 0, 20, 36)])
 def test_convolution_rotation_append_kernel(dtype, taps, rot, pairing, hd, hdv):
     """Three sequences fed in two steps (the second reads the first's last values from the ring, for one sequence a
     single new token, for one more tokens than taps) against the plain convolution and rotation of the whole sequences."""
@@ -284,7 +285,7 @@ def test_convolution_rotation_append_kernel(dtype, taps, rot, pairing, hd, hdv):
         pos = torch.from_numpy(np.concatenate([np.arange(l, h) for l, h in zip(lo, hi)]).astype(np.int32)).to(DEV)
         cu = torch.from_numpy(np.concatenate([[0], np.cumsum(new)]).astype(np.int32)).to(DEV)
         q_out = torch.empty(sum(new), nh * hd, dtype=dtype, device=DEV)
-        ops.conv_rope_append(qkv, w.to(DEV) if taps else None, ring, slots, cu, torch.tensor(hi, dtype=torch.int32, device=DEV),
+        ops.conv_rope_append(qkv, w.t().contiguous().to(DEV) if taps else None, ring, slots, cu, torch.tensor(hi, dtype=torch.int32, device=DEV),
                              q_out, k_d, v_d, seq, pos, tab, inv, nh, nkv, rot, pairing, True, status)
         for b, part in enumerate(torch.split(q_out.float().cpu(), new)):
             q_got[b].append(part)
