@@ -101,48 +101,88 @@ moe_route_kernel(const float* __restrict__ logits, int* __restrict__ chosen, flo
 }
 
 // The router's product and the routing in one kernel.  A block takes TOK tokens: their activations go to shared memory
-// as floats; warp w forms the logits of experts w, w + 8, ...: its lanes stride over K (a weight row is read once per block,
-// 128 bytes per warp and load), each lane keeps one partial sum per token, added over k = lane, lane + 32, ... in
-// ascending order and then across the lanes by a fixed tree, so a logit depends on its token and expert alone.  Then warp
-// w routes token w.  Everything in float.  smem: x [TOK][K], logits [TOK][E + n_groups].
-template <int TOK, typename TX>
-__global__ void __launch_bounds__(256)
+// as floats; warp w forms the logits of experts w, w + warps, ...: its lanes stride over K four elements at a time (a weight
+// row is read once per block, 512 bytes per warp and load), each lane keeps one partial sum per token, added over its k in
+// ascending order and then across the lanes by a fixed tree, so a logit depends on its token and expert alone.  Then a warp
+// routes each token.  Everything in float.  K a multiple of 4.  smem: x [TOK][K], logits [TOK][E + n_groups].
+// Few tokens (decode): one token a block and 32 warps, so that a token's experts are spread over many warps.
+template <int TOK, int THREADS, typename TX>
+__global__ void __launch_bounds__(THREADS)
 moe_router_kernel(const TX* __restrict__ x, const float* __restrict__ wr, int* __restrict__ chosen, float* __restrict__ weight,
                   int T, int K, int E, int top, int n_groups, int keep, int renorm, int ldx) {
     ik_pdl_wait();
     IK_AFTER_WAIT(x);
     ik_pdl_launch_dependents();
-    extern __shared__ float sm[];
+    extern __shared__ __align__(16) float sm[];
     const int ng = n_groups > 1 ? n_groups : 0;
     float* xs = sm;                                   // [TOK][K]
     float* lg = sm + (size_t)TOK * K;                 // [TOK][E + ng]
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int t0 = blockIdx.x * TOK;
-    for (int idx = threadIdx.x; idx < TOK * K; idx += 256) {
-        const int i = idx / K, k = idx - i * K;
-        xs[idx] = t0 + i < T ? ik_ld(x, (size_t)(t0 + i) * ldx + k) : 0.f;
-    }
-    __syncthreads();
-    for (int e = warp; e < E; e += 8) {
-        const float* w = wr + (size_t)e * K;
-        float acc[TOK];
-        #pragma unroll
-        for (int i = 0; i < TOK; i++) acc[i] = 0.f;
+    constexpr int V = 16 / (int)sizeof(TX);            // activations per 16-byte load
+    if (K % V == 0 && ldx % V == 0 && ((uintptr_t)x % 16) == 0) {
+        const int KV = K / V;
         #pragma unroll 4
-        for (int k = lane; k < K; k += 32) {
-            const float wv = __ldg(w + k);
-            #pragma unroll
-            for (int i = 0; i < TOK; i++) acc[i] = fmaf(xs[i * K + k], wv, acc[i]);
+        for (int idx = threadIdx.x; idx < TOK * KV; idx += THREADS) {
+            const int i = idx / KV, kv = idx - i * KV;
+            float* dst = xs + (size_t)i * K + kv * V;
+            if (t0 + i < T) {
+                const uint4 raw = *reinterpret_cast<const uint4*>(x + (size_t)(t0 + i) * ldx + kv * V);
+                const TX* e = reinterpret_cast<const TX*>(&raw);
+                #pragma unroll
+                for (int j = 0; j < V; j++) dst[j] = ik_ld(e, j);
+            } else {
+                #pragma unroll
+                for (int j = 0; j < V; j++) dst[j] = 0.f;
+            }
         }
-        #pragma unroll
-        for (int i = 0; i < TOK; i++) {
-            float v = acc[i];
-            for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
-            if (lane == 0) lg[i * (E + ng) + e] = v;
+    } else {
+        for (int idx = threadIdx.x; idx < TOK * K; idx += THREADS) {
+            const int i = idx / K, k = idx - i * K;
+            xs[idx] = t0 + i < T ? ik_ld(x, (size_t)(t0 + i) * ldx + k) : 0.f;
         }
     }
     __syncthreads();
-    for (int i = warp; i < TOK; i += 8) {
+    const int K4 = K >> 2;
+    const float4* xs4 = reinterpret_cast<const float4*>(xs);
+    // four experts a pass: an activation read from shared memory serves four products
+    constexpr int EB = 4, NW = THREADS / 32;
+    for (int e0 = warp; e0 < E; e0 += NW * EB) {
+        const float4* w4[EB];
+        #pragma unroll
+        for (int j = 0; j < EB; j++) w4[j] = reinterpret_cast<const float4*>(wr + (size_t)min(e0 + j * NW, E - 1) * K);
+        float acc[EB][TOK];
+        #pragma unroll
+        for (int j = 0; j < EB; j++)
+            #pragma unroll
+            for (int i = 0; i < TOK; i++) acc[j][i] = 0.f;
+        #pragma unroll 2
+        for (int k = lane; k < K4; k += 32) {
+            float4 wv[EB];
+            #pragma unroll
+            for (int j = 0; j < EB; j++) wv[j] = (j == 0 || e0 + j * NW < E) ? __ldg(w4[j] + k) : make_float4(0.f, 0.f, 0.f, 0.f);
+            #pragma unroll
+            for (int i = 0; i < TOK; i++) {
+                const float4 xv = xs4[i * K4 + k];
+                #pragma unroll
+                for (int j = 0; j < EB; j++)
+                    acc[j][i] = fmaf(xv.w, wv[j].w, fmaf(xv.z, wv[j].z, fmaf(xv.y, wv[j].y, fmaf(xv.x, wv[j].x, acc[j][i]))));
+            }
+        }
+        #pragma unroll
+        for (int j = 0; j < EB; j++) {
+            const int e = e0 + j * NW;
+            if (e >= E) break;
+            #pragma unroll
+            for (int i = 0; i < TOK; i++) {
+                float v = acc[j][i];
+                for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+                if (lane == 0) lg[i * (E + ng) + e] = v;
+            }
+        }
+    }
+    __syncthreads();
+    for (int i = warp; i < TOK; i += THREADS / 32) {
         const int t = t0 + i;
         if (t >= T) continue;
         float* sc = lg + (size_t)i * (E + ng);
@@ -375,24 +415,27 @@ IK_EXPORT int ik_moe_router(const void* x, int x_dtype, const float* wr, int* ch
                             int n_groups, int keep, int renorm, int ldx, cudaStream_t stream) {
     if (T < 0 || E <= 0 || K <= 0 || top <= 0 || top > E || ldx < K) return IK_BAD_ARGUMENT;
     if (n_groups > 1 && (E % n_groups || keep <= 0 || keep > n_groups || top > keep * (E / n_groups))) return IK_BAD_ARGUMENT;
+    if (K % 4 || ((uintptr_t)wr % 16)) return IK_UNSUPPORTED;
     if (T == 0) return IK_OK;
     const int ng = n_groups > 1 ? n_groups : 0;
-    // few tokens (decode): a block per token, so that the step's tokens spread over the SMs; else eight tokens a block
-    const int tok = T <= 64 ? 1 : 8;
+    // few tokens (decode): a block per token, so that the step's tokens spread over the SMs; else eight tokens a block,
+    // or four where eight rows of activations would leave room for one block per SM only
+    const int tok = T <= 64 ? 1 : K <= 2048 ? 8 : K <= 6144 ? 4 : 1;
     const size_t smem = ((size_t)tok * K + (size_t)tok * (E + ng)) * sizeof(float);
     if (smem > 200 * 1024) return IK_UNSUPPORTED;
 #define IK_ROUTER(TOK, TX)                                                                                                 \
     {                                                                                                                      \
-        auto kern = moe_router_kernel<TOK, TX>;                                                                            \
+        constexpr int THREADS = TOK == 1 ? 1024 : 256;                                                                     \
+        auto kern = moe_router_kernel<TOK, THREADS, TX>;                                                                          \
         if (smem > 48 * 1024) {                                                                                            \
             cudaError_t e0 = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);           \
             if (e0 != cudaSuccess) return (int)e0;                                                                         \
         }                                                                                                                  \
-        IK_RETURN_IF_ERROR(ik_launch(kern, (T + TOK - 1) / TOK, 256, smem, stream, (const TX*)x, wr, chosen, weight, T, K, E, top, \
+        IK_RETURN_IF_ERROR(ik_launch(kern, (T + TOK - 1) / TOK, THREADS, smem, stream, (const TX*)x, wr, chosen, weight, T, K, E, top, \
                                      n_groups, keep, renorm, ldx));                                                        \
     }
-    if (x_dtype == IK_F32) { if (tok == 1) IK_ROUTER(1, float) else IK_ROUTER(8, float) }
-    else if (x_dtype == IK_BF16) { if (tok == 1) IK_ROUTER(1, __nv_bfloat16) else IK_ROUTER(8, __nv_bfloat16) }
+    if (x_dtype == IK_F32) { if (tok == 1) IK_ROUTER(1, float) else if (tok == 4) IK_ROUTER(4, float) else IK_ROUTER(8, float) }
+    else if (x_dtype == IK_BF16) { if (tok == 1) IK_ROUTER(1, __nv_bfloat16) else if (tok == 4) IK_ROUTER(4, __nv_bfloat16) else IK_ROUTER(8, __nv_bfloat16) }
     else return IK_BAD_ARGUMENT;
 #undef IK_ROUTER
     IK_LAUNCH_STATUS();

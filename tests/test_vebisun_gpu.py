@@ -511,3 +511,45 @@ def test_greedy_generation_through_the_engine(models, name, graphs):
             if float(top2[0] - top2[1]) > 1e-4 * float(lg.abs().max()):
                 assert tok == int(lg.argmax()), (len(p), i)
     assert eng.cache.table.n_slots_in_use() == 0
+
+
+# ------------------------------------------------------------------------------------------ the programs
+def test_trace_replay_and_command_line(models, tmp_path):
+    """bin/trace_run on a batch of unequal prompts decoded together, against the plain implementation; bin/ithaca
+    describes the looped schedule and generates greedily what the engine generates."""
+    import subprocess
+    import sys
+    from helpers import ROOT
+    d, V = models["A"], CFG_A["vocab"]
+    reqs = {"p": random_ids(70, V, 90), "q": random_ids(3, V, 91), "r": random_ids(130, V, 92)}
+    steps = [{"step": 0, "entries": [{"id": "p", "tokens": reqs["p"][:66], "want": [0, 65]}, {"id": "q", "tokens": reqs["q"][:1], "want": []},
+                                     {"id": "r", "tokens": reqs["r"][:126], "want": [125]}], "end": []}]
+    for i in range(4):
+        ent = [{"id": "p", "tokens": [reqs["p"][66 + i]], "want": [0]}, {"id": "r", "tokens": [reqs["r"][126 + i]], "want": [0]}]
+        if i < 2:
+            ent.insert(1, {"id": "q", "tokens": [reqs["q"][1 + i]], "want": [0] if i == 1 else []})
+        steps.append({"step": 1 + i, "entries": ent, "end": (["q"] if i == 1 else []) + (["p", "r"] if i == 3 else [])})
+    out = tmp_path / "out"
+    p = subprocess.run([sys.executable, os.path.join(ROOT, "bin", "trace_run"), "--model", d, "--dtype", "float32", "--out", str(out),
+                        "--max-tokens", "210"], input="".join(json.dumps(s) + "\n" for s in steps), capture_output=True, text=True,
+                       timeout=600)
+    assert p.returncode == 0, p.stderr[-3000:]
+    assert [l for l in p.stdout.splitlines() if l.startswith("done ")] == [f"done {i}" for i in range(5)]
+    want = {r: _plain(d, ids) for r, ids in reqs.items()}
+    got0 = np.fromfile(out / "0.f32", dtype="<f4").reshape(3, V)
+    assert rel_err(got0, np.stack([want["p"][0], want["p"][65], want["r"][125]])) < REL["float32"]
+    got2 = np.fromfile(out / "2.f32", dtype="<f4").reshape(3, V)
+    assert rel_err(got2, np.stack([want["p"][67], want["q"][2], want["r"][127]])) < REL["float32"]
+    got4 = np.fromfile(out / "4.f32", dtype="<f4").reshape(2, V)
+    assert rel_err(got4, np.stack([want["p"][69], want["r"][129]])) < REL["float32"]
+
+    cli = [sys.executable, os.path.join(ROOT, "bin", "ithaca"), "--model", d, "--dtype", "float32"]
+    p = subprocess.run(cli + ["--describe"], capture_output=True, text=True, timeout=600)
+    assert p.returncode == 0 and p.stdout.count("sandwich") == 7 and p.stdout.count("input added first") == 2, p.stderr[-2000:]
+    prompt = random_ids(11, V, 93)
+    p = subprocess.run(cli + ["--prompt", ",".join(map(str, prompt)), "-n", "5", "--rep-pen", "1.0", "--stop-ids", ""],
+                       capture_output=True, text=True, timeout=600)
+    assert p.returncode == 0, p.stderr[-2000:]
+    from ithaca_b200 import Engine
+    eng = Engine(d, dtype="float32", max_tokens=512)
+    assert [int(x) for x in p.stdout.strip().split(",")] == eng.generate([prompt], max_tokens=5, temp=0.0, rep_pen=1.0, stop_token_ids=[])[0]
