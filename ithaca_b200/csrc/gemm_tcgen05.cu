@@ -147,14 +147,22 @@ struct Walk {
                 item += gridDim.x;
                 if (!groups) break;
                 int g;
-                asm volatile("ld.global.s32 %0, [%1];" : "=r"(g) : "l"(groups + w.tile % tiles_m) : "memory");
+                asm volatile("ld.global.s32 %0, [%1];" : "=r"(g) : "l"(groups + w.tile / tiles_n) : "memory");
                 if (g >= 0) { w.group = g; break; }
             }
             w.kb0 = w.z * kb_per_split;
             w.nkb = min(kb_per_split, nkb_total - w.kb0);
         }
-        w.mt = w.tile % tiles_m;
-        w.nt = w.tile / tiles_m;
+        if (groups) {
+            // grouped: the weight tiles of one token tile follow one another, so the blocks at work at one time share a
+            // few token tiles and the matrices of a few groups (all of which stay in L2), instead of one weight tile of
+            // every group and nearly all token tiles
+            w.mt = w.tile / tiles_n;
+            w.nt = w.tile % tiles_n;
+        } else {
+            w.mt = w.tile % tiles_m;
+            w.nt = w.tile / tiles_m;
+        }
         w.first = w.kb0 == 0;
         w.last = w.kb0 + w.nkb == nkb_total;
         return true;
