@@ -494,7 +494,7 @@ def marginal_run(eng, cfg, batch, vocab, context, steps=30):
 # window, layers, (loop start, stop, times)).
 VEBISUN_SIZES = [
     ("2048 wide, 32 experts of 1024, 4 chosen", 2048, 16, 4, 128, 32, 4, 1024, 4, 2, 1024, 4, (1, 3, 2)),
-    ("4096 wide, 16 experts of 3584, 2 chosen", 4096, 32, 8, 128, 16, 2, 3584, 2, 1, 2048, 3, (0, 1, 2)),
+    ("4096 wide, 16 experts of 3584, 2 chosen", 4096, 32, 8, 128, 16, 2, 3584, 4, 2, 2048, 3, (0, 1, 2)),
 ]
 
 
@@ -502,7 +502,7 @@ def vebisun_pair(size, vocab=32000):
     """The Vebisun configuration of a size and the Llama next to it: the same width, heads and head size, as many layers
     as the Vebisun model has layer runs, a feed-forward as wide as the experts a token uses together, the same window."""
     _, d, nh, nkv, hd, E, top, ff, ng, keep, window, layers, loop = size
-    mixer = {"heads": nh, "kv_heads": nkv, "dim": hd, "vdim": hd, "conv": 4, "scale": hd ** -0.5, "softcap": 50.0,
+    mixer = {"heads": nh, "kv_heads": nkv, "dim": hd, "vdim": hd, "conv": 4, "scale": hd ** -0.5, "softcap": 30.0,
              "mask": {"size": window},
              "rot": {"base": 500000.0, "dims": hd // 2, "scaling": {"factor": 8.0, "low": 1.0, "high": 4.0, "original": 8192}}}
     mlp = {"kind": "moe", "expert": {"ff": ff}, "router": {"experts": E, "top": top, "groups": {"count": ng, "keep": keep}}}
