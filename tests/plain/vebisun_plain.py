@@ -22,7 +22,7 @@ The design in this file's notation (T tokens, width d):
 from __future__ import annotations
 
 import math
-from typing import Dict, List, Mapping, Sequence
+from typing import List, Mapping, Sequence
 
 import torch
 

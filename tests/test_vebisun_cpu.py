@@ -1,9 +1,7 @@
 """Vebisun without a device: the configuration reader, the description built from it, the tensors it asks
 for, a random model folder read back, and the plain implementation's parts against closed forms."""
 import copy
-import json
 import math
-import os
 
 import pytest
 import torch

@@ -7,7 +7,6 @@ prompts and in decoding, long decoding, and greedy generation through the engine
 weights would hide a fault (a window one key off, a far key), the weights are made so that one key decides
 the result.
 """
-import copy
 import json
 import os
 
@@ -468,7 +467,6 @@ def test_the_one_key_that_matters(tmp_path, window, conv, dtype):
     if window:
         places += [n - 1 - window, n - window, n - window + 1, n - 1 - 64, n - 64]
     hay = [3 + (i * 7) % 37 for i in range(n)]
-    seen = []
     for at in sorted(set(p for p in places if 0 <= p < n - 1)):
         ids = list(hay)
         ids[at], ids[n - 1] = 1, 2
@@ -483,7 +481,6 @@ def test_the_one_key_that_matters(tmp_path, window, conv, dtype):
             # rounding of 16 bits (0.4 % of 5) into a layer norm over otherwise small components: up to 3 % of the
             # logits' scale, the same for every cutting; a wrong key moves them by 30 % (checked below)
             assert rel_err(lg.cpu().numpy()[0], want) < (REL[dtype] if dtype == "float32" else 6e-2), (at, cut)
-        seen.append(float(np.abs(want).max()))
     eng.check_status()
     if window:                                                     # the test has teeth: inside and outside differ widely
         ids_in, ids_out = list(hay), list(hay)
