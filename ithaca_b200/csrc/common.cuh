@@ -47,6 +47,17 @@ __device__ __forceinline__ float ik_swiglu(float g, float u) { return g / (1.0f 
 // rounded to bfloat16 anyway.
 __device__ __forceinline__ float ik_swiglu_fast(float g, float u) { return g * __frcp_rn(1.0f + __expf(-g)) * u; }
 
+// The gated activation with its constants as parameters: g <- min(g, limit) and u <- clamp(u, -limit, limit) when
+// limit > 0; g * sigmoid(alpha g) * (u + shift).
+__device__ __forceinline__ float ik_glu(float g, float u, float alpha, float limit, float shift) {
+    if (limit > 0.f) { g = fminf(g, limit); u = fminf(fmaxf(u, -limit), limit); }
+    return g * (1.0f / (1.0f + expf(-alpha * g))) * (u + shift);
+}
+__device__ __forceinline__ float ik_glu_fast(float g, float u, float alpha, float limit, float shift) {
+    if (limit > 0.f) { g = fminf(g, limit); u = fminf(fmaxf(u, -limit), limit); }
+    return g * __frcp_rn(1.0f + __expf(-alpha * g)) * (u + shift);
+}
+
 // Value a float would have after a round trip through the storage type.
 template <typename T> __device__ __forceinline__ float ik_round_to(float v);
 template <> __device__ __forceinline__ float ik_round_to<float>(float v) { return v; }

@@ -131,6 +131,93 @@ IK_EXPORT int ik_rmsnorm(const float* x, const int* rows_in, const float* w, voi
     IK_LAUNCH_STATUS();
 }
 
+// ------------------------------------------------------------------ RMS norm behind a sublayer
+// residual += mult * scale * (y * (1 / sqrt(mean(y^2) + eps)) * w), one block per row; `scale` (a vector, "layer scale")
+// may be absent.  When `copy` is given it receives the new residual row in its own type: the next sublayer's input
+// where sublayers read the stream itself.
+template <typename TC>
+__global__ void __launch_bounds__(256)
+rmsnorm_add_kernel(const float* __restrict__ y, const float* __restrict__ w, const float* __restrict__ scale,
+                   float* __restrict__ residual, TC* __restrict__ copy, int d, float eps, float mult) {
+    ik_pdl_wait();
+    IK_AFTER_WAIT(y);
+    ik_pdl_launch_dependents();
+    __shared__ float red[32];
+    const float* a = y + (size_t)blockIdx.x * d;
+    float* res = residual + (size_t)blockIdx.x * d;
+    float ss = 0.f;
+    for (int i = threadIdx.x; i < d; i += 256) { float v = a[i]; ss = fmaf(v, v, ss); }
+    ss = ik_block_sum<256>(ss, red);
+    const float s = 1.0f / sqrtf(ss / (float)d + eps);
+    for (int i = threadIdx.x; i < d; i += 256) {
+        float v = a[i] * s * w[i];
+        if (scale) v *= scale[i];
+        const float r = res[i] + mult * v;
+        res[i] = r;
+        if (copy) ik_st(copy, (size_t)blockIdx.x * d + i, r);
+    }
+}
+
+IK_EXPORT int ik_rmsnorm_add(const float* y, const float* w, const float* scale, float* residual, void* copy, int copy_dtype,
+                             int rows, int d, float eps, float mult, cudaStream_t stream) {
+    if (rows < 0 || d <= 0 || !y || !w || !residual) return IK_BAD_ARGUMENT;
+    if (rows == 0) return IK_OK;
+    if (copy && copy_dtype == IK_BF16)
+        IK_RETURN_IF_ERROR(ik_launch(rmsnorm_add_kernel<__nv_bfloat16>, rows, 256, 0, stream, y, w, scale, residual, (__nv_bfloat16*)copy, d, eps, mult));
+    else if (!copy || copy_dtype == IK_F32)
+        IK_RETURN_IF_ERROR(ik_launch(rmsnorm_add_kernel<float>, rows, 256, 0, stream, y, w, scale, residual, (float*)copy, d, eps, mult));
+    else
+        return IK_BAD_ARGUMENT;
+    IK_LAUNCH_STATUS();
+}
+
+// ------------------------------------------------------------------ cast
+// out[r, c] = in[r * ld_in + c] for c < cols, float to the output's type (a column range of a wider float matrix as the
+// next product's operand).
+template <typename TO>
+__global__ void cast_kernel(const float* __restrict__ in, int ld_in, TO* __restrict__ out, int ld_out, int cols, size_t total) {
+    ik_pdl_wait();
+    IK_AFTER_WAIT(in);
+    ik_pdl_launch_dependents();
+    const size_t stride = (size_t)gridDim.x * blockDim.x;
+    for (size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x; idx < total; idx += stride) {
+        const size_t r = idx / cols, c = idx - r * cols;
+        ik_st(out, r * ld_out + c, in[r * ld_in + c]);
+    }
+}
+
+IK_EXPORT int ik_cast(const float* in, int ld_in, void* out, int out_dtype, int ld_out, int rows, int cols, cudaStream_t stream) {
+    if (rows < 0 || cols <= 0 || ld_in < cols || ld_out < cols) return IK_BAD_ARGUMENT;
+    if (rows == 0) return IK_OK;
+    const size_t total = (size_t)rows * cols;
+    const int blocks = (int)((total + 255) / 256 < 65535 * 16 ? (total + 255) / 256 : 65535 * 16);
+    if (out_dtype == IK_F32) IK_RETURN_IF_ERROR(ik_launch(cast_kernel<float>, blocks, 256, 0, stream, in, ld_in, (float*)out, ld_out, cols, total));
+    else if (out_dtype == IK_BF16) IK_RETURN_IF_ERROR(ik_launch(cast_kernel<__nv_bfloat16>, blocks, 256, 0, stream, in, ld_in, (__nv_bfloat16*)out, ld_out, cols, total));
+    else return IK_BAD_ARGUMENT;
+    IK_LAUNCH_STATUS();
+}
+
+// ------------------------------------------------------------------ logit scale and cap
+// v <- v * scale, then cap * tanh(v / cap) when cap > 0, in place.
+__global__ void scale_softcap_kernel(float* __restrict__ v, size_t n, float scale, float cap) {
+    ik_pdl_wait();
+    IK_AFTER_WAIT(v);
+    ik_pdl_launch_dependents();
+    const size_t stride = (size_t)gridDim.x * blockDim.x;
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += stride) {
+        float x = v[i] * scale;
+        if (cap > 0.f) x = cap * tanhf(x / cap);
+        v[i] = x;
+    }
+}
+
+IK_EXPORT int ik_scale_softcap(float* v, unsigned long long n, float scale, float cap, cudaStream_t stream) {
+    if (n == 0) return IK_OK;
+    const int blocks = (int)((n + 255) / 256 < 65535 * 16 ? (n + 255) / 256 : 65535 * 16);
+    IK_RETURN_IF_ERROR(ik_launch(scale_softcap_kernel, blocks, 256, 0, stream, v, (size_t)n, scale, cap));
+    IK_LAUNCH_STATUS();
+}
+
 // ------------------------------------------------------------------ SwiGLU
 // in: [T, 2*ff] float; gate in columns [0, ff) and up in [ff, 2ff), or, interleaved, gate j in column
 // 2j and up j in column 2j + 1.  out[t, j] = silu(g) * u.
@@ -158,6 +245,38 @@ IK_EXPORT int ik_swiglu(const float* gate_up, void* out, int out_dtype, int T, i
         IK_RETURN_IF_ERROR(ik_launch(swiglu_kernel<float>, blocks, 256, 0, stream, gate_up, (float*)out, ff, total, interleaved));
     else if (out_dtype == IK_BF16)
         IK_RETURN_IF_ERROR(ik_launch(swiglu_kernel<__nv_bfloat16>, blocks, 256, 0, stream, gate_up, (__nv_bfloat16*)out, ff, total, interleaved));
+    else
+        return IK_BAD_ARGUMENT;
+    IK_LAUNCH_STATUS();
+}
+
+// The gated activation with its constants as parameters: g <- min(g, limit), u <- clamp(u, -limit, limit) (limit > 0),
+// out = g * sigmoid(alpha g) * (u + shift).  silu(g) * u is alpha = 1, no limit, shift = 0.
+template <typename TO>
+__global__ void glu_kernel(const float* __restrict__ gu, TO* __restrict__ out, int ff, size_t total, int interleaved,
+                           float alpha, float limit, float shift) {
+    ik_pdl_wait();
+    IK_AFTER_WAIT(gu);
+    ik_pdl_launch_dependents();
+    const size_t stride = (size_t)gridDim.x * blockDim.x;
+    for (size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x; idx < total; idx += stride) {
+        const size_t t = idx / ff, j = idx - t * ff;
+        const float* row = gu + t * 2 * ff;
+        const float g = interleaved ? row[2 * j] : row[j], u = interleaved ? row[2 * j + 1] : row[ff + j];
+        ik_st(out, idx, ik_glu(g, u, alpha, limit, shift));
+    }
+}
+
+IK_EXPORT int ik_glu_act(const float* gate_up, void* out, int out_dtype, int T, int ff, int interleaved, float alpha, float limit,
+                         float shift, cudaStream_t stream) {
+    if (T < 0 || ff <= 0) return IK_BAD_ARGUMENT;
+    if (T == 0) return IK_OK;
+    const size_t total = (size_t)T * ff;
+    const int blocks = (int)((total + 255) / 256 < 65535 * 16 ? (total + 255) / 256 : 65535 * 16);
+    if (out_dtype == IK_F32)
+        IK_RETURN_IF_ERROR(ik_launch(glu_kernel<float>, blocks, 256, 0, stream, gate_up, (float*)out, ff, total, interleaved, alpha, limit, shift));
+    else if (out_dtype == IK_BF16)
+        IK_RETURN_IF_ERROR(ik_launch(glu_kernel<__nv_bfloat16>, blocks, 256, 0, stream, gate_up, (__nv_bfloat16*)out, ff, total, interleaved, alpha, limit, shift));
     else
         return IK_BAD_ARGUMENT;
     IK_LAUNCH_STATUS();

@@ -41,12 +41,16 @@ def gemm(x: torch.Tensor, w: torch.Tensor, out: Optional[torch.Tensor] = None, a
     return out
 
 
-def gemm_swiglu(x: torch.Tensor, w_interleaved: torch.Tensor, out_dtype: torch.dtype = torch.bfloat16) -> torch.Tensor:
+def gemm_swiglu(x: torch.Tensor, w_interleaved: torch.Tensor, out_dtype: torch.dtype = torch.bfloat16, glu=None) -> torch.Tensor:
     """h = silu(x Wg^T) * (x Wu^T) in one kernel.  ``w_interleaved``: [2 ff, d] with gate j in row 2j and
     up j in row 2j + 1, so that a product tile holds both halves of every pair it covers and the
-    [tokens, 2 ff] intermediate is never written."""
+    [tokens, 2 ff] intermediate is never written.  ``glu``: (alpha, limit, shift) of the gate with parameters,
+    g * sigmoid(alpha g) * (u + shift) with g and u clamped by ``limit``; None = silu(g) * u."""
     M, ff = x.shape[0], w_interleaved.shape[0] // 2
     out = torch.empty((M, ff), dtype=out_dtype, device=x.device)
+    if glu is not None:
+        gu = gemm(x, w_interleaved, out_dtype=torch.float32)
+        return ops.glu_act(gu, out_dtype, *glu, out=out, interleaved=True)
     if takes_skinny(M, w_interleaved.shape[0], w_interleaved.shape[1]):
         done = ops.gemm_bf16_mma(x, w_interleaved, out=out, kind=1, swiglu=True)
     else:

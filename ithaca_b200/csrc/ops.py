@@ -104,6 +104,17 @@ _SIGNATURES = {
     "ik_gemm_tcgen05_issue_rate": [_i, _i, _i, _vp, _vp, _vp],
     "ik_gemm_tcgen05_take_wait_record": [_vp],
     "ik_sample": [_vp, _i, _vp, _vp, _i, _i, _f, _i, _f, _f, _vp, _i, _u64, _vp, _vp, _vp],
+    "ik_rmsnorm_add": [_vp, _vp, _vp, _vp, _vp, _i, _i, _i, _f, _f, _vp],
+    "ik_cast": [_vp, _i, _vp, _i, _i, _i, _i, _vp],
+    "ik_scale_softcap": [_vp, _u64, _f, _f, _vp],
+    "ik_glu_act": [_vp, _vp, _i, _i, _i, _i, _f, _f, _f, _vp],
+    "ik_causal_conv": [_vp, _i, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _i, _vp],
+    "ik_selective_scan": [_vp, _i, _vp, _vp, _vp, _vp, _i, _i, _i, _vp, _vp, _i, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _vp],
+    "ik_decay_attention": [_vp, _i, _i, _i, _i, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _vp],
+    "ik_norm_rope_append": [_vp, _i, _i, _i, _i, _vp, _vp, _f, _vp, _i, _vp, _vp, _i, _vp, _vp, _vp, _i, _vp, _f, _i, _i, _i, _i,
+                            _i, _i, _i, _i, _i, _i, _vp, _vp],
+    "ik_head_gate": [_vp, _vp, _i, _i, _vp, _i, _i, _i, _i, _i, _f, _vp],
+    "ik_gated_rmsnorm": [_vp, _vp, _vp, _i, _i, _vp, _i, _i, _i, _i, _f, _f, _vp],
 }
 
 _lib = None
@@ -894,4 +905,214 @@ def sample(logits: torch.Tensor, temperature: float, top_k: int, top_p: float, r
     _check(lib().ik_sample(_ptr(logits), logits.stride(0), _ptr(work), _ptr(out), rows, V, temperature, top_k, top_p,
                            repetition_penalty, _ptr(recent), n_recent, seed & 0xFFFFFFFFFFFFFFFF, _ptr(streams),
                            _ptr(counters), _stream()), "sample")
+    return out
+
+
+# ---------------------------------------------------------------------------------------------
+# Norm behind a sublayer, casts, the gated activation with parameters, logit scale and cap
+def rmsnorm_add(y: torch.Tensor, weight: torch.Tensor, eps: float, residual: torch.Tensor, scale: Optional[torch.Tensor] = None,
+                mult: float = 1.0, copy: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """residual += mult * scale * rmsnorm(y) * weight (``scale``: a vector or None).  ``copy`` (the residual's shape, any
+    kernel type) receives the new residual."""
+    _need(y, "y", torch.float32)
+    _need(weight, "weight", torch.float32)
+    _need(residual, "residual", torch.float32)
+    d = y.shape[-1]
+    if weight.numel() != d or residual.shape != y.shape or (scale is not None and scale.numel() != d):
+        raise KernelError("rmsnorm_add: the sizes do not fit together")
+    if scale is not None:
+        _need(scale, "scale", torch.float32)
+    if copy is not None:
+        _need(copy, "copy")
+        if copy.shape != y.shape:
+            raise KernelError("rmsnorm_add: the copy must have the residual's shape")
+    rows = y.numel() // d
+    _work(f"rmsnorm +add {rows}x{d}", rows * d * 12 + _nbytes(copy))
+    _check(lib().ik_rmsnorm_add(_ptr(y), _ptr(weight), _ptr(scale), _ptr(residual), _ptr(copy), _code(copy) if copy is not None else F32,
+                                rows, d, eps, mult, _stream()), "rmsnorm_add")
+    return residual
+
+
+def cast(x: torch.Tensor, out_dtype: torch.dtype, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """A float matrix (rows may be wider apart than their length: a column range) in another type, rows contiguous."""
+    _need(x, "x", torch.float32, contiguous=False)
+    rows, cols = x.shape
+    if x.stride(1) != 1:
+        raise KernelError("cast: rows must be contiguous")
+    if out is None:
+        out = torch.empty((rows, cols), dtype=out_dtype, device=x.device)
+    _need(out, "out")
+    _work(f"cast {rows}x{cols}", rows * cols * (4 + out.element_size()))
+    _check(lib().ik_cast(_ptr(x), x.stride(0), _ptr(out), _code(out), cols, rows, cols, _stream()), "cast")
+    return out
+
+
+def scale_softcap_(v: torch.Tensor, scale: float, cap: float) -> torch.Tensor:
+    """v <- v * scale, then cap * tanh(v / cap) when cap > 0 (float, in place)."""
+    _need(v, "v", torch.float32)
+    _work(f"scale_softcap {v.numel()}", 8 * v.numel())
+    _check(lib().ik_scale_softcap(_ptr(v), v.numel(), scale, cap, _stream()), "scale_softcap")
+    return v
+
+
+def glu_act(gate_up: torch.Tensor, out_dtype: torch.dtype, alpha: float, limit: float, shift: float,
+            out: Optional[torch.Tensor] = None, interleaved: bool = False) -> torch.Tensor:
+    """g <- min(g, limit), u <- clamp(u, -limit, limit) (limit > 0); g * sigmoid(alpha g) * (u + shift)."""
+    _need(gate_up, "gate_up", torch.float32)
+    T, ff2 = gate_up.shape
+    if ff2 % 2:
+        raise KernelError("glu_act: the input needs an even number of columns (gate then up)")
+    if out is None:
+        out = torch.empty((T, ff2 // 2), dtype=out_dtype, device=gate_up.device)
+    _work(f"glu_act {T}x{ff2 // 2}", _nbytes(gate_up, out))
+    _check(lib().ik_glu_act(_ptr(gate_up), _ptr(out), _code(out), T, ff2 // 2, 1 if interleaved else 0, alpha, limit, shift, _stream()),
+           "glu_act")
+    return out
+
+
+# ---------------------------------------------------------------------------------------------
+# Mixers with a state of fixed size
+def causal_conv(x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor], ring: Optional[torch.Tensor], ctx,
+                out_dtype: torch.dtype, act: bool = True) -> torch.Tensor:
+    """Causal convolution over time per channel with bias and silu.  ``x`` [T, C] float (rows may be a column range),
+    ``w`` [taps, C] tap-major, ``ring`` [max_slots, taps, C] float: each sequence's last inputs, brought up to date."""
+    _need(x, "x", torch.float32, contiguous=False)
+    _need(w, "w", torch.float32)
+    T, C = x.shape
+    taps = w.shape[0]
+    if w.shape[1] != C or x.stride(1) != 1 or (bias is not None and bias.numel() != C):
+        raise KernelError("causal_conv: the sizes do not fit together")
+    if taps > 1:
+        _need(ring, "ring", torch.float32)
+        if tuple(ring.shape[1:]) != (taps, C):
+            raise KernelError("causal_conv: the ring has the wrong shape")
+    out = torch.empty((T, C), dtype=out_dtype, device=x.device)
+    _work(f"causal_conv {T}x{C}", T * C * (4 + out.element_size()))
+    _check(lib().ik_causal_conv(_ptr(x), x.stride(0), _ptr(w), _ptr(bias), _ptr(ring) if taps > 1 else 0, _ptr(ctx.slots),
+                                _ptr(ctx.cu_seqlens), _ptr(ctx.kv_lens), _ptr(ctx.token_seq), _ptr(ctx.token_pos), _ptr(out),
+                                _code(out), T, ctx.n_seqs, C, taps, 1 if act else 0, 1 if ctx.is_decode else 0, _stream()),
+           "causal_conv", kernels=1 if ctx.is_decode or taps == 1 else 2)
+    return out
+
+
+def selective_scan(u: torch.Tensor, dt_raw: torch.Tensor, dt_bias: Optional[torch.Tensor], A: torch.Tensor, bc: torch.Tensor,
+                   b_off: int, c_off: int, D: Optional[torch.Tensor], z: Optional[torch.Tensor], state: torch.Tensor, ctx,
+                   out_dtype: torch.dtype) -> torch.Tensor:
+    """The selective scan over the step's tokens, sequence by sequence.  ``u`` [T, inner], ``dt_raw`` [T, inner] float
+    (before bias and softplus), ``A`` [inner, N] float (negative), B and C = columns ``b_off``.. and ``c_off``.. of ``bc``,
+    ``z`` [T, inner] float (rows may be a column range) for the gate y * silu(z), ``state`` [max_slots, 2, inner, N] float."""
+    _need(u, "u")
+    _need(dt_raw, "dt_raw", torch.float32)
+    _need(A, "A", torch.float32)
+    _need(bc, "bc", torch.float32, contiguous=False)
+    _need(state, "state", torch.float32)
+    T, inner = u.shape
+    N = A.shape[1]
+    if A.shape[0] != inner or dt_raw.shape != (T, inner) or tuple(state.shape[1:]) != (2, inner, N) or bc.stride(1) != 1 \
+            or max(b_off, c_off) + N > bc.shape[1]:
+        raise KernelError("selective_scan: the sizes do not fit together")
+    ldz = 0
+    if z is not None:
+        _need(z, "z", torch.float32, contiguous=False)
+        if z.shape != (T, inner) or z.stride(1) != 1:
+            raise KernelError("selective_scan: the gate has the wrong shape")
+        ldz = z.stride(0)
+    out = torch.empty((T, inner), dtype=out_dtype, device=u.device)
+    _work(f"selective_scan {T}x{inner}x{N}", T * inner * (u.element_size() + 8 + out.element_size()) + 8 * ctx.n_seqs * inner * N,
+          9 * T * inner * N)
+    st = lib().ik_selective_scan(_ptr(u), _code(u), _ptr(dt_raw), _ptr(dt_bias), _ptr(A), _ptr(bc), bc.stride(0), b_off, c_off,
+                                 _ptr(D), _ptr(z), ldz, _ptr(state), _ptr(ctx.slots), _ptr(ctx.cu_seqlens), _ptr(ctx.kv_lens),
+                                 _ptr(out), _code(out), T, ctx.n_seqs, inner, N, _stream())
+    _check(st, "selective_scan")
+    return out
+
+
+def decay_attention(p: torch.Tensor, q_off: int, k_off: int, v_off: int, decay: torch.Tensor, state: torch.Tensor, ctx,
+                    n_heads: int, dk: int, dv: int, act: bool = True) -> torch.Tensor:
+    """Linear attention with one constant decay per head: S <- a S + k v^T, o = S^T q, over the step's tokens.  q, k, v
+    are column ranges of ``p`` (float), passed through silu when ``act``.  ``state`` [max_slots, 2, heads, dk, dv] float.
+    Returns float [T, heads * dv]."""
+    _need(p, "p", torch.float32, contiguous=False)
+    _need(decay, "decay", torch.float32)
+    _need(state, "state", torch.float32)
+    T = p.shape[0]
+    if decay.numel() != n_heads or tuple(state.shape[1:]) != (2, n_heads, dk, dv) or p.stride(1) != 1 \
+            or max(q_off + n_heads * dk, k_off + n_heads * dk, v_off + n_heads * dv) > p.shape[1]:
+        raise KernelError("decay_attention: the sizes do not fit together")
+    out = torch.empty((T, n_heads * dv), dtype=torch.float32, device=p.device)
+    _work(f"decay_attention {T}x{n_heads}x{dk}x{dv}", T * n_heads * (2 * dk + 2 * dv) * 4 + 8 * ctx.n_seqs * n_heads * dk * dv,
+          4 * T * n_heads * dk * dv)
+    _check(lib().ik_decay_attention(_ptr(p), p.stride(0), q_off, k_off, v_off, _ptr(decay), _ptr(state), _ptr(ctx.slots),
+                                    _ptr(ctx.cu_seqlens), _ptr(ctx.kv_lens), _ptr(out), T, ctx.n_seqs, n_heads, dk, dv,
+                                    1 if act else 0, _stream()), "decay_attention")
+    return out
+
+
+# ---------------------------------------------------------------------------------------------
+# Around an attention core whose projections come out of one wide product
+def norm_rope_append(p: torch.Tensor, q_off: int, k_off: int, v_off: int, q_w: Optional[torch.Tensor], k_w: Optional[torch.Tensor],
+                     eps: float, q_out: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Tensor, token_seq: torch.Tensor,
+                     token_pos: torch.Tensor, table: torch.Tensor, inv_freq: Optional[torch.Tensor], magnitude: float,
+                     n_heads: int, rotary_dim: int, pairing: int, write_cache: bool, status: Optional[torch.Tensor]) -> None:
+    """RMS norm of q and of k over their whole projections (``q_w``, ``k_w``: weights of that size; None = no norm),
+    rotation of each head's leading ``rotary_dim`` dimensions with cos and sin times ``magnitude``, q to ``q_out``,
+    k and v into the pages.  q, k, v are column ranges of ``p`` (float)."""
+    _need(p, "p", torch.float32, contiguous=False)
+    _need(q_out, "q_out")
+    _need(k_pages, "k_pages")
+    _need(v_pages, "v_pages")
+    _need(table, "table", torch.int32)
+    n_pages, nkv, page_size, hd = k_pages.shape
+    hdv = v_pages.shape[3]
+    T = p.shape[0]
+    if p.stride(1) != 1 or q_out.shape != (T, n_heads * hd) or v_pages.shape[:3] != k_pages.shape[:3] or v_pages.dtype != k_pages.dtype \
+            or max(q_off + n_heads * hd, k_off + nkv * hd, v_off + nkv * hdv) > p.shape[1] \
+            or (q_w is not None and q_w.numel() != n_heads * hd) or (k_w is not None and k_w.numel() != nkv * hd):
+        raise KernelError("norm_rope_append: the sizes do not fit together")
+    _work(f"norm_rope_append {T}", T * ((n_heads + nkv) * hd + nkv * hdv) * 4 + _nbytes(q_out) + T * nkv * (hd + hdv) * k_pages.element_size())
+    _check(lib().ik_norm_rope_append(_ptr(p), p.stride(0), q_off, k_off, v_off, _ptr(q_w), _ptr(k_w), eps, _ptr(q_out), _code(q_out),
+                                     _ptr(k_pages), _ptr(v_pages), _code(k_pages), _ptr(token_seq), _ptr(token_pos), _ptr(table),
+                                     table.stride(0), _ptr(inv_freq), magnitude, T, n_heads, nkv, hd, hdv, rotary_dim, pairing,
+                                     page_size, n_pages, 1 if write_cache else 0, _ptr(status), _stream()), "norm_rope_append")
+
+
+def head_gate(att: torch.Tensor, p: Optional[torch.Tensor], g_off: int, out: torch.Tensor, n_heads: int, mult: float = 1.0) -> torch.Tensor:
+    """out[t, h, :] = att[t, h, :] * sigmoid(p[t, g_off + h]) * mult (``p`` None: no gate); ``out`` may be a column range of
+    a wider matrix."""
+    _need(att, "att")
+    _need(out, "out", att.dtype, contiguous=False)
+    T, cols = att.shape
+    ldp = 0
+    if p is not None:
+        _need(p, "p", torch.float32, contiguous=False)
+        if p.stride(1) != 1 or g_off + n_heads > p.shape[1]:
+            raise KernelError("head_gate: the gate has the wrong shape")
+        ldp = p.stride(0)
+    if cols % n_heads or out.shape != att.shape or out.stride(1) != 1:
+        raise KernelError("head_gate: the sizes do not fit together")
+    _work(f"head_gate {T}x{cols}", 2 * _nbytes(att))
+    _check(lib().ik_head_gate(_ptr(att), _ptr(p), ldp, g_off, _ptr(out), _code(att), out.stride(0), T, n_heads,
+                              cols // n_heads, mult, _stream()), "head_gate")
+    return out
+
+
+def gated_rmsnorm(x: torch.Tensor, weight: torch.Tensor, eps: float, p: Optional[torch.Tensor], g_off: int, out: torch.Tensor,
+                  mult: float = 1.0) -> torch.Tensor:
+    """out = rmsnorm(x) * weight * sigmoid(p[:, g_off : g_off + d]) * mult (no gate when ``p`` is None); ``out`` may be a column
+    range of a wider matrix."""
+    _need(x, "x", torch.float32)
+    _need(weight, "weight", torch.float32)
+    _need(out, "out", contiguous=False)
+    rows, d = x.shape
+    ldp = 0
+    if p is not None:
+        _need(p, "p", torch.float32, contiguous=False)
+        if p.stride(1) != 1 or g_off + d > p.shape[1]:
+            raise KernelError("gated_rmsnorm: the gate has the wrong shape")
+        ldp = p.stride(0)
+    if weight.numel() != d or out.shape != x.shape or out.stride(1) != 1:
+        raise KernelError("gated_rmsnorm: the sizes do not fit together")
+    _work(f"gated_rmsnorm {rows}x{d}", rows * d * (8 + out.element_size()))
+    _check(lib().ik_gated_rmsnorm(_ptr(x), _ptr(weight), _ptr(p), ldp, g_off, _ptr(out), _code(out), out.stride(0), rows, d, eps,
+                                  mult, _stream()), "gated_rmsnorm")
     return out

@@ -87,10 +87,12 @@ class DecoderModel:
         """Runs the step's tokens through every scheduled run; returns float32 logits
         [wanted rows, vocab], or None when no row is wanted."""
         h = self.embedding.forward(ctx.token_ids, ctx)
+        ctx.shared.pop("stream_copy", None)                    # nothing of an earlier pass over this description counts
         h0 = h.clone() if any(e.adds_input for e in self.spec.schedule) else None
         for e in self.spec.schedule:
             if e.adds_input:
                 ops.add_(h, h0)
+                ctx.shared.pop("stream_copy", None)            # a block's 16-bit copy of the stream is stale now
             self.layers[e.layer].forward(h, ctx, cache.layer(e.cache), e.writes_cache)
         if ctx.n_logit_rows == 0:
             return None

@@ -20,6 +20,17 @@ Options a spec may give (all off by default):
   convolution over time on every channel of q, k and v, directly behind the projections and in
   front of the rotation.  The last projected values of a sequence are part of its state: a ring
   of ``taps`` positions per sequence beside its pages (``StateRequest``).
+* ``qk_norm: "projection"`` with the tensors ``q_norm``, ``k_norm``: q and k are RMS-normed over their whole
+  projections (all heads at once, ``norm_eps`` inside the root) with weights of that size, before the rotation.
+* ``head_gate`` with the tensor ``g`` [n_heads, hidden]: every head's result is multiplied by the sigmoid of one
+  number per head, a projection of the mixer's input, before the output projection.
+* a position part whose cos and sin carry a constant factor (``magnitude``).
+
+With one of the last three the mixer runs "wide": one product gives [q | k | v | g] in float, one kernel norms, rotates
+and appends, the attention kernel runs, and the gate kernel writes the output projection's operand.  A wide mixer can
+also serve as a branch of a composite (``parts/parallel.py``): ``branch_in()`` / ``branch_out()`` hand out its matrices
+so that the composite stacks them with other branches' into one product each, and ``core`` works on column ranges of
+those products' matrices.
 """
 from __future__ import annotations
 
@@ -32,7 +43,7 @@ from ..cache.cache import KVRequest, LayerCache, StateRequest
 from ..config.spec import PartSpec
 from ..csrc import ops
 from ..weights.loader import TensorReq
-from .base import Runtime, register_mixer
+from .base import Runtime, as_float32, register_mixer
 from .linear import Linear
 
 
@@ -46,6 +57,11 @@ class Attention:
         hdv = spec.get("v_head_dim") or hd
         out = {w["q"]: TensorReq((nh * hd, d)), w["k"]: TensorReq((nkv * hd, d)),
                w["v"]: TensorReq((nkv * hdv, d)), w["o"]: TensorReq((d, nh * hdv))}
+        if spec.get("qk_norm"):
+            out[w["q_norm"]] = TensorReq((nh * hd,), init="ones")
+            out[w["k_norm"]] = TensorReq((nkv * hd,), init="ones")
+        if spec.get("head_gate"):
+            out[w["g"]] = TensorReq((nh, d))
         taps = spec.get("conv_taps") or 0
         if taps:
             # taps around 1/taps: the convolution keeps the projections' scale
@@ -53,7 +69,8 @@ class Attention:
                 out[w[role]] = TensorReq((rows, taps), std=1.0 / taps)
         return out
 
-    def __init__(self, spec: PartSpec, tensors: Mapping[str, torch.Tensor], runtime: Runtime, position=None):
+    def __init__(self, spec: PartSpec, tensors: Mapping[str, torch.Tensor], runtime: Runtime, position=None,
+                 standalone: bool = True):
         self.hidden = int(spec["hidden_size"])
         self.n_heads = int(spec["n_heads"])
         self.n_kv_heads = int(spec["n_kv_heads"])
@@ -75,21 +92,41 @@ class Attention:
             raise ValueError("attention: the rotated width exceeds the head size")
         w = spec.weights
         wq, wk = tensors[w["q"]], tensors[w["k"]]
+        qk_norm = spec.get("qk_norm")
+        if qk_norm not in (None, "projection"):
+            raise ValueError(f"attention: qk_norm {qk_norm!r} is not supported (projection)")
+        self.head_gate = bool(spec.get("head_gate"))
+        self.wide = bool(qk_norm or self.head_gate or (position is not None and getattr(position, "magnitude", 1.0) != 1.0)
+                         or not standalone)
+        if self.wide and self.conv_taps:
+            raise ValueError("attention: a short convolution and the wide arrangement (qk_norm, head_gate) do not go together")
+        self.norm_eps = float(spec.get("norm_eps") or 0.0)
+        self.q_norm_w = as_float32(tensors[w["q_norm"]], runtime) if qk_norm else None
+        self.k_norm_w = as_float32(tensors[w["k_norm"]], runtime) if qk_norm else None
         # bfloat16 path with the whole head rotated: the rows of the q and k weights are reordered so that the
         # two members of a rotary pair are neighbours, (i, i + hd/2) -> (2i, 2i + 1).  Scores do not change (q and k
         # are reordered alike, and the cache holds k in that order); the product's epilogue can then rotate a pair
         # and write q and the cache entries itself, without the [tokens, q+k+v] intermediate.
         self.pairing = position.pairing if position is not None else 0
         self.fused_rope = (runtime.dtype == "bfloat16" and position is not None and position.rotary_dim == self.head_dim
-                           and self.head_dim % 2 == 0 and not self.conv_taps and self.v_head_dim == self.head_dim)
+                           and self.head_dim % 2 == 0 and not self.conv_taps and self.v_head_dim == self.head_dim
+                           and not self.wide)
         if self.fused_rope and self.pairing == 0:
             half = self.head_dim // 2
             order = torch.stack((torch.arange(half), torch.arange(half) + half), dim=1).reshape(-1)
             wq = wq.view(self.n_heads, self.head_dim, -1)[:, order].reshape(wq.shape)
             wk = wk.view(self.n_kv_heads, self.head_dim, -1)[:, order].reshape(wk.shape)
             self.pairing = 1                                       # pairs are (2i, 2i + 1) from here on
-        self.qkv = Linear([wq, wk, tensors[w["v"]]], runtime)
-        self.o = Linear([tensors[w["o"]]], runtime)
+        self._in = [wq, wk, tensors[w["v"]]] + ([tensors[w["g"]]] if self.head_gate else [])
+        self._out = tensors[w["o"]]
+        self.k_off = self.n_heads * self.head_dim
+        self.v_off = self.k_off + self.n_kv_heads * self.head_dim
+        self.g_off = self.v_off + self.n_kv_heads * self.v_head_dim
+        self.n_in = self.g_off + (self.n_heads if self.head_gate else 0)
+        self.n_mid = self.n_heads * self.v_head_dim
+        if standalone:
+            self.qkv = Linear(self._in, runtime)
+            self.o = Linear([self._out], runtime)
         self.runtime = runtime
         self.conv_weight = None
         self.channels = (self.n_heads + self.n_kv_heads) * self.head_dim + self.n_kv_heads * self.v_head_dim
@@ -97,7 +134,29 @@ class Attention:
             cw = torch.cat([tensors[w[r]].to(torch.float32) for r in ("q_conv", "k_conv", "v_conv")], dim=0)
             self.conv_weight = cw.to(runtime.device).t().contiguous()              # tap-major [taps, channels]: a tap's weights of neighbouring channels lie together
         # the plain path (projections, then convolution, rotation and append in one kernel) serves every option
-        self.plain_append = bool(self.conv_taps) or self.v_head_dim != self.head_dim
+        self.plain_append = (bool(self.conv_taps) or self.v_head_dim != self.head_dim) and not self.wide
+
+    # -- as a branch of a composite mixer ------------------------------------------------------
+    def branch_in(self):
+        """The matrices whose products with the mixer's input ``core`` reads, in the order of its columns."""
+        return list(self._in)
+
+    def branch_out(self):
+        """The matrix that multiplies what ``core`` writes."""
+        return self._out
+
+    def core(self, p: torch.Tensor, mid: torch.Tensor, ctx, cache: LayerCache, writes_cache: bool = True, mult: float = 1.0) -> None:
+        """``p`` [T, n_in] float: [q | k | v | g] (a column range of a wider matrix may be given); ``mid`` [T, n_mid] in the
+        activation type receives ``mult`` times the gated heads, the operand of the output projection."""
+        rt, pos = self.runtime, self.position
+        q = torch.empty((p.shape[0], self.n_heads * self.head_dim), dtype=rt.act_dtype, device=p.device)
+        table = ctx.tables[cache.kv_group]
+        ops.norm_rope_append(p, 0, self.k_off, self.v_off, self.q_norm_w, self.k_norm_w, self.norm_eps, q, cache.k_pages,
+                             cache.v_pages, ctx.token_seq, ctx.token_pos, table, pos.inv_freq if pos is not None else None,
+                             getattr(pos, "magnitude", 1.0), self.n_heads, pos.rotary_dim if pos is not None else 0,
+                             self.pairing, writes_cache, rt.status)
+        att = attend(q, cache, ctx, table, self.n_heads, self.scale, self.window or 0, rt, self.softcap)
+        ops.head_gate(att, p if self.head_gate else None, self.g_off, mid, self.n_heads, mult)
 
     def cache_requests(self) -> List[object]:
         v = self.v_head_dim if self.v_head_dim != self.head_dim else None
@@ -111,6 +170,12 @@ class Attention:
         """``accumulate=False``: the output replaces what ``residual`` holds instead of adding to it."""
         rt = self.runtime
         T = x.shape[0]
+        if self.wide:
+            p = self.qkv(x, out_dtype=torch.float32)
+            mid = torch.empty((T, self.n_mid), dtype=rt.act_dtype, device=x.device)
+            self.core(p, mid, ctx, cache, writes_cache)
+            self.o(mid, out=residual, accumulate=accumulate)
+            return
         q = torch.empty((T, self.n_heads * self.head_dim), dtype=rt.act_dtype, device=x.device)
         table = ctx.tables[cache.kv_group]
         pos = self.position

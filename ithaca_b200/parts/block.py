@@ -8,6 +8,11 @@ and the parts add into it, so the sum never passes through 16 bits.
 stream: x += m * norm_out(mixer(norm(x))); x += m * norm_out'(feed_forward(norm'(x))).  The
 sublayer writes into a float32 buffer of its own (the stream is not what it adds to); the norm
 behind it scales and adds in one kernel.  The feed-forward may be absent.
+
+``outnorm``: a norm behind each sublayer only: x += norm_out(mixer(x)); x += norm_out'(feed_forward(x)).  The
+sublayers read the stream itself.  On the 16-bit path their operand is a 16-bit copy of the stream, which the
+norm's kernel writes beside the float stream it adds to (the next sublayer's input, also across layers), so no
+kernel exists only to convert.  The feed-forward may be absent.
 """
 from __future__ import annotations
 
@@ -18,6 +23,7 @@ import torch
 
 from ..cache.cache import LayerCache
 from ..config.spec import BlockSpec
+from ..csrc import ops
 from ..weights.loader import TensorReq
 from .base import BLOCKS, FEED_FORWARDS, MIXERS, NORMS, POSITIONS, Runtime, register_block
 
@@ -120,5 +126,77 @@ class SandwichBlock:
             self.ff_out_norm.add_into(y, residual, self.mult)
 
 
+class OutNormBlock:
+    COPY = "stream_copy"        # in StepContext.shared: the stream in the activation type, as of the last add
+
+    @classmethod
+    def manifest(cls, spec: BlockSpec) -> Dict[str, TensorReq]:
+        out: Dict[str, TensorReq] = {}
+        _merge(out, MIXERS.get(spec.mixer.kind).manifest(spec.mixer))
+        if spec.feed_forward is not None:
+            _merge(out, FEED_FORWARDS.get(spec.feed_forward.kind).manifest(spec.feed_forward))
+        for name, n in spec.norms.items():
+            if spec.feed_forward is None and name.startswith("feed_forward"):
+                continue
+            _merge(out, NORMS.get(n.kind).manifest(n))
+        if spec.position is not None:
+            _merge(out, POSITIONS.get(spec.position.kind).manifest(spec.position))
+        return out
+
+    def __init__(self, spec: BlockSpec, tensors: Mapping[str, torch.Tensor], runtime: Runtime):
+        has_ff = spec.feed_forward is not None
+        for need in ("mixer_out",) + (("feed_forward_out",) if has_ff else ()):
+            if need not in spec.norms:
+                raise ValueError(f"outnorm block: the spec has no '{need}' norm")
+        self.runtime = runtime
+        position = None
+        if spec.position is not None:
+            position = POSITIONS.get(spec.position.kind)(spec.position, tensors, runtime)
+        mixer_cls = MIXERS.get(spec.mixer.kind)
+        if "position" in inspect.signature(mixer_cls.__init__).parameters:
+            self.mixer = mixer_cls(spec.mixer, tensors, runtime, position=position)
+        else:
+            self.mixer = mixer_cls(spec.mixer, tensors, runtime)
+        self.feed_forward = FEED_FORWARDS.get(spec.feed_forward.kind)(spec.feed_forward, tensors, runtime) if has_ff else None
+
+        def norm(name):
+            n = spec.norms[name]
+            made = NORMS.get(n.kind)(n, tensors, runtime)
+            if "copy" not in inspect.signature(getattr(made, "add_into", lambda: None)).parameters:
+                raise ValueError(f"outnorm block: norm kind '{n.kind}' cannot stand behind a sublayer and hand the stream on")
+            return made
+
+        self.mixer_out_norm = norm("mixer_out")
+        self.ff_out_norm = norm("feed_forward_out") if has_ff else None
+
+    def cache_requests(self) -> List[object]:
+        return list(self.mixer.cache_requests())
+
+    def _operand(self, residual: torch.Tensor, ctx) -> torch.Tensor:
+        """What a sublayer multiplies: the stream itself in float32, its 16-bit copy otherwise."""
+        if self.runtime.act_dtype == torch.float32:
+            return residual
+        x = ctx.shared.pop(self.COPY, None)
+        return x if x is not None else ops.cast(residual, self.runtime.act_dtype)
+
+    def _fresh_copy(self, residual: torch.Tensor):
+        return None if self.runtime.act_dtype == torch.float32 else torch.empty_like(residual, dtype=self.runtime.act_dtype)
+
+    def forward(self, residual: torch.Tensor, ctx, cache: LayerCache, writes_cache: bool = True) -> None:
+        y = torch.empty_like(residual)
+        self.mixer.forward(self._operand(residual, ctx), ctx, cache, y, writes_cache, accumulate=False)
+        copy = self._fresh_copy(residual)
+        self.mixer_out_norm.add_into(y, residual, copy=copy)
+        if copy is not None:
+            ctx.shared[self.COPY] = copy
+        if self.feed_forward is not None:
+            self.feed_forward.forward(self._operand(residual, ctx), ctx, y, accumulate=False)
+            copy = self._fresh_copy(residual)
+            self.ff_out_norm.add_into(y, residual, copy=copy)
+            if copy is not None:
+                ctx.shared[self.COPY] = copy
+
+
 register_block("prenorm", PreNormBlock)
 register_block("sandwich", SandwichBlock)
+register_block("outnorm", OutNormBlock)

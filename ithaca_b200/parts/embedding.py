@@ -3,7 +3,8 @@
 x[t, :] = E[id_t, :] * scale (src/model.cpp:1381-1383).  The reference clamps an id
 outside the vocabulary; here the step function rejects it before anything runs.
 logits = W_out xn, where W_out is the embedding matrix when the model has no
-output matrix of its own (src/model.cpp:132, 1590-1592).
+output matrix of its own (src/model.cpp:132, 1590-1592).  A head may scale its logits by a constant
+(``scale``) and cap them, cap * tanh(logit / cap) (``softcap``), both in float.
 """
 from __future__ import annotations
 
@@ -42,9 +43,14 @@ class OutputHead:
     def __init__(self, spec: PartSpec, tensors: Mapping[str, torch.Tensor], runtime: Runtime):
         self.vocab_size = int(spec["vocab_size"])
         self.linear = Linear([tensors[spec.weights["weight"]]], runtime)
+        self.scale = float(spec.get("scale") or 1.0)
+        self.softcap = float(spec.get("softcap") or 0.0)
 
     def forward(self, xn: torch.Tensor) -> torch.Tensor:
-        return self.linear(xn, out_dtype=torch.float32)
+        logits = self.linear(xn, out_dtype=torch.float32)
+        if self.scale != 1.0 or self.softcap > 0.0:
+            ops.scale_softcap_(logits, self.scale, self.softcap)
+        return logits
 
 
 register_embedding("embedding", Embedding)

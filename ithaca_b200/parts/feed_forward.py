@@ -1,7 +1,10 @@
 """Gated feed-forward: g = Wg x, u = Wu x, h = act(g) * u, y = Wd h, added to the
 residual stream (src/model.cpp:1559-1565; silu(x) = x / (1 + exp(-x)), :1309).
 Gate and up are stacked into one product ([gate; up], the split the reference
-applies to a fused ``ffn_up``, src/model.cpp:1553-1557)."""
+applies to a fused ``ffn_up``, src/model.cpp:1553-1557).
+
+``activation: "swish"`` is the same arrangement with the gate's constants as parameters: g <- min(g, limit) and
+u <- clamp(u, -limit, limit) when ``limit`` is given, then h = g * sigmoid(alpha g) * (u + up_shift)."""
 from __future__ import annotations
 
 from typing import Dict, Mapping
@@ -26,8 +29,11 @@ class GatedMLP:
 
     def __init__(self, spec: PartSpec, tensors: Mapping[str, torch.Tensor], runtime: Runtime):
         act = spec.get("activation", "silu")
-        if act != "silu":
-            raise ValueError(f"gated_mlp: activation {act!r} is not supported (silu)")
+        if act not in ("silu", "swish"):
+            raise ValueError(f"gated_mlp: activation {act!r} is not supported (silu, swish)")
+        # None: silu(g) * u by the kernels that have always done it; else (alpha, limit or 0, shift)
+        self.glu = None if act == "silu" else (float(spec.get("alpha", 1.0)), float(spec.get("limit") or 0.0),
+                                               float(spec.get("up_shift", 0.0)))
         self.hidden = int(spec["hidden_size"])
         self.intermediate = int(spec["intermediate_size"])
         w = spec.weights
@@ -45,10 +51,10 @@ class GatedMLP:
     def forward(self, x: torch.Tensor, ctx, residual: torch.Tensor, accumulate: bool = True) -> None:
         if self.fused:
             from ..csrc import gemm_bf16
-            h = gemm_bf16.gemm_swiglu(x, self.gate_up.weight, self.runtime.act_dtype)
+            h = gemm_bf16.gemm_swiglu(x, self.gate_up.weight, self.runtime.act_dtype, glu=self.glu)
         else:
             gu = self.gate_up(x, out_dtype=torch.float32)
-            h = ops.swiglu(gu, self.runtime.act_dtype)
+            h = ops.swiglu(gu, self.runtime.act_dtype) if self.glu is None else ops.glu_act(gu, self.runtime.act_dtype, *self.glu)
         self.down(h, out=residual, accumulate=accumulate)
 
 

@@ -3,7 +3,8 @@
 
 Layer norm: y = (x - mean) / sqrt(var + eps) * w + b with var the mean of the squared
 deviations, in float32.  A norm may also stand behind a sublayer: ``add_into`` then adds
-``mult * y`` to the residual stream in the same kernel."""
+``mult * y`` to the residual stream in the same kernel.  The RMS norm may carry a second vector
+(``scale``, a per-channel "layer scale") that multiplies what it adds to the stream."""
 from __future__ import annotations
 
 from typing import Dict, Mapping, Optional
@@ -19,17 +20,25 @@ from .base import Runtime, as_float32, register_norm
 class RMSNorm:
     @classmethod
     def manifest(cls, spec: PartSpec) -> Dict[str, TensorReq]:
-        return {spec.weights["weight"]: TensorReq((spec["size"],), init="ones")}
+        out = {spec.weights["weight"]: TensorReq((spec["size"],), init="ones")}
+        if "scale" in spec.weights:
+            out[spec.weights["scale"]] = TensorReq((spec["size"],), init="ones")
+        return out
 
     def __init__(self, spec: PartSpec, tensors: Mapping[str, torch.Tensor], runtime: Runtime):
         self.size = int(spec["size"])
         self.eps = float(spec["eps"])
         self.weight = as_float32(tensors[spec.weights["weight"]], runtime)
+        self.scale = as_float32(tensors[spec.weights["scale"]], runtime) if "scale" in spec.weights else None
         self.runtime = runtime
 
     def forward(self, x: torch.Tensor, rows: Optional[torch.Tensor] = None,
                 out_dtype: Optional[torch.dtype] = None) -> torch.Tensor:
         return ops.rmsnorm(x, self.weight, self.eps, out_dtype or self.runtime.act_dtype, rows_in=rows)
+
+    def add_into(self, x: torch.Tensor, residual: torch.Tensor, mult: float = 1.0, copy: Optional[torch.Tensor] = None) -> None:
+        """residual += mult * scale * norm(x); ``copy`` receives the new residual in its own type."""
+        ops.rmsnorm_add(x, self.weight, self.eps, residual, scale=self.scale, mult=mult, copy=copy)
 
 
 class LayerNorm:

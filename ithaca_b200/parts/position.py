@@ -11,6 +11,12 @@ regime to the other.  The table is computed once in float64 and rounded to
 float32; the angle pos * inv_freq[i] is formed in float32 by the kernel, as the
 reference forms it on the host (src/model.cpp:698-713).
 
+The ``yarn`` rule blends by dimension instead of by wavelength: D(t) = rot ln(original / (2 pi t)) / (2 ln theta) is
+the (fractional) dimension whose frequency makes t turns over the original context; with lo = max(floor(D(fast_turns)), 0)
+and hi = min(ceil(D(slow_turns)), rot - 1), pair i gets the weight clamp((i - lo) / max(hi - lo, 0.001), 0, 1) and the
+frequency f_i / factor * weight + f_i * (1 - weight).  Under this rule cos and sin are also enlarged by the constant
+0.1 ln(factor) + 1 (``magnitude``; 1 for every other rule), which the kernels that rotate take as a parameter.
+
 Pairing: ``half`` rotates (i, i + rot/2), ``interleaved`` rotates (2i, 2i+1); the
 reference has both behind its ``neox`` flag (src/model.cpp:643).
 """
@@ -55,9 +61,26 @@ def inverse_frequencies(rotary_dim: int, theta: float, scaling) -> np.ndarray:
                 mix = (r - low) / (high - low)
                 out[n] = (1.0 - mix) * f / factor + mix * f
         freq = out
+    elif kind == "yarn":
+        factor, original = float(scaling["factor"]), float(scaling["original_max_position_embeddings"])
+
+        def dimension(turns: float) -> float:
+            return rotary_dim * math.log(original / (2.0 * math.pi * turns)) / (2.0 * math.log(float(theta)))
+        lo = max(math.floor(dimension(float(scaling["fast_turns"]))), 0)
+        hi = min(math.ceil(dimension(float(scaling["slow_turns"]))), rotary_dim - 1)
+        weight = np.clip((np.arange(rotary_dim // 2, dtype=np.float64) - lo) / max(hi - lo, 0.001), 0.0, 1.0)
+        freq = freq / factor * weight + freq * (1.0 - weight)
     else:
-        raise ValueError(f"rotary: scaling type {kind!r} is not supported (llama3, linear, default)")
+        raise ValueError(f"rotary: scaling type {kind!r} is not supported (llama3, linear, yarn, default)")
     return freq.astype(np.float32)
+
+
+def magnitude(scaling) -> float:
+    """What cos and sin are multiplied by: 0.1 ln(factor) + 1 under the ``yarn`` rule, else 1."""
+    kind = None if not scaling else scaling.get("rope_type", scaling.get("type"))
+    if kind == "yarn":
+        return 0.1 * math.log(float(scaling["factor"])) + 1.0
+    return 1.0
 
 
 _TABLES: Dict[tuple, torch.Tensor] = {}      # one device copy per distinct table: layers with equal settings share it
@@ -80,6 +103,7 @@ class RotaryPosition:
             table = inverse_frequencies(self.rotary_dim, float(spec["theta"]), scaling)
             _TABLES[self.key] = torch.from_numpy(table).to(runtime.device)
         self.inv_freq = _TABLES[self.key]
+        self.magnitude = magnitude(scaling)
 
 
 register_position("rotary", RotaryPosition)
