@@ -6,6 +6,9 @@
     python bench.py --only vebisun [--batch B]                  the Vebisun decoder at a few sizes beside a Llama of equal width,
                                                                 heads and active feed-forward size: prefill and decode tok/s and
                                                                 every kernel's fraction of the device's peaks
+    python bench.py --only tiralix [--batch B]                  the Tiralix decoder (selective scan and parallel softmax / decayed linear
+                                                                attention layers) at a few sizes beside a Llama of equal width, heads,
+                                                                feed-forward and depth, in the same form
     python bench.py --config 1b-unequal|13b-long                the other two workloads alone, through Engine.generate
 
 Prints ONE JSON line.  ``value`` is decoded tokens per second at the given batch with every
@@ -517,7 +520,37 @@ def vebisun_pair(size, vocab=32000):
     return veb, llama, runs
 
 
-def vebisun_run(pk, batch, steps, warmup, context=2048, prompt=4096):
+TIRALIX_SIZES = [
+    # name, width, heads, kv heads, head size, feed-forward, scan channels, scan states, step-size rank, layers
+    ("2048 wide, 16 heads of 128, scan of 4096 x 16", 2048, 16, 4, 128, 8192, 4096, 16, 128, ("mamba1", "parallel", "parallel", "mamba1")),
+    ("4096 wide, 32 heads of 128, scan of 8192 x 16", 4096, 32, 8, 128, 14336, 8192, 16, 256, ("mamba1", "parallel", "parallel", "mamba1")),
+]
+
+
+def tiralix_pair(size, vocab=32000):
+    """The Tiralix configuration of a size and the Llama next to it: the same width, heads, head size, feed-forward width
+    and number of layers."""
+    _, d, nh, nkv, hd, ff, inner, N, R, kinds = size
+    par = {"left": {"heads": nh, "kv_heads": nkv, "dim": hd, "vdim": hd, "scale": hd ** -0.5,
+                    "rot": {"base": 500000.0, "dims": hd // 2, "scaling": {"factor": 8.0, "original": 8192, "fast": 32.0, "slow": 1.0}}},
+           "right": {"heads": nh, "dim": hd, "vdim": hd, "decay": [1.0 - 2.0 ** -(3 + 5 * h / max(nh - 1, 1)) for h in range(nh)]},
+           "left_scale": 0.7, "right_scale": 0.7}
+    scan = {"inner": inner, "state": N, "dt_rank": R, "conv": 4}
+    mlp = {"kind": "dense", "ff": ff, "limit": 7.0}
+    tir = {"architecture": "Tiralix", "vocab": vocab, "width": d, "norm": {"eps": 1e-6}, "logit_scale": 1.0, "logit_softcap": 30.0,
+           "layers": [{"type": k, "mixer": par if k == "parallel" else scan, "mlp": mlp} for k in kinds]}
+    llama = {"architectures": ["LlamaForCausalLM"], "hidden_size": d, "num_hidden_layers": len(kinds), "num_attention_heads": nh,
+             "num_key_value_heads": nkv, "head_dim": hd, "intermediate_size": ff, "vocab_size": vocab, "rope_theta": 500000.0,
+             "rope_scaling": None, "rms_norm_eps": 1e-6, "max_position_embeddings": 131072, "tie_word_embeddings": True,
+             "torch_dtype": "bfloat16"}
+    return tir, llama, len(kinds)
+
+
+def tiralix_run(pk, batch, steps, warmup, context=2048, prompt=4096):
+    return vebisun_run(pk, batch, steps, warmup, context, prompt, sizes=TIRALIX_SIZES, pair=tiralix_pair, name="tiralix")
+
+
+def vebisun_run(pk, batch, steps, warmup, context=2048, prompt=4096, sizes=None, pair=None, name="vebisun"):
     """Per size and model: tok/s of one prompt of ``prompt`` tokens, tok/s of graph-replayed decode steps at ``batch``
     sequences of ``context`` positions, and per kernel of a prompt step and of a decode step its time and its better
     fraction of the two peaks (bytes over the copy bandwidth, operations over the bfloat16 product rate)."""
@@ -526,10 +559,10 @@ def vebisun_run(pk, batch, steps, warmup, context=2048, prompt=4096):
     import torch
     from ithaca_b200 import Engine
     out = []
-    for size in VEBISUN_SIZES:
-        veb, llama, runs = vebisun_pair(size)
+    for size in (sizes or VEBISUN_SIZES):
+        veb, llama, runs = (pair or vebisun_pair)(size)
         row = {"size": size[0], "layer_runs": runs, "prompt": prompt, "decode_batch": batch, "decode_context": context}
-        for name, cfg in (("vebisun", veb), ("llama", llama)):
+        for model, cfg in ((name, veb), ("llama", llama)):
             vocab = cfg.get("vocab", cfg.get("vocab_size"))
             eng = Engine.from_random(cfg, seed=0, dtype="bfloat16", max_tokens=(batch + 1) * (max(context, prompt) + 128),
                                      ctx=max(context, prompt) + 128, max_step_tokens=max(16384, prompt))
@@ -555,7 +588,7 @@ def vebisun_run(pk, batch, steps, warmup, context=2048, prompt=4096):
             dec_rows = kernels(slots, [[2] for _ in slots])
             for s in slots:
                 eng.free_slot(s)
-            row[name] = {"prefill_tok_s": round(prompt / (pre_ms / 1e3), 1), "prefill_ms": round(pre_ms, 3),
+            row[model] = {"prefill_tok_s": round(prompt / (pre_ms / 1e3), 1), "prefill_ms": round(pre_ms, 3),
                          "decode_tok_s": round(dec["tok_s"], 1), "decode_ms_per_step": round(dec["ms_per_step"], 4),
                          "decode_launches": dec["launches_per_step"], "weight_gb": round(eng.model.weight_bytes() / 1e9, 3),
                          "prefill_kernels": pre_rows, "decode_kernels": dec_rows}
@@ -609,7 +642,7 @@ def main():
                     help="with --only decode / prefill: another context length (decode) or prompt length (prefill) than the default run's")
     ap.add_argument("--config", default=None, choices=["1b-unequal", "13b-long"],
                     help="run one of the other workloads alone and print its figures")
-    ap.add_argument("--only", default="all", choices=["all", "decode", "prefill", "attention", "products", "marginal", "issue-rate", "vebisun"],
+    ap.add_argument("--only", default="all", choices=["all", "decode", "prefill", "attention", "products", "marginal", "issue-rate", "vebisun", "tiralix"],
                     help="run one part only and print its figures (for profiling a small case)")
     args = ap.parse_args()
 
@@ -635,6 +668,9 @@ def main():
     cfg = dict(shape_cfg)
     if args.only == "vebisun":
         print(json.dumps({"only": "vebisun", "peaks": pk, "sizes": vebisun_run(pk, args.batch, min(args.steps, 64), args.warmup)}))
+        return 0
+    if args.only == "tiralix":
+        print(json.dumps({"only": "tiralix", "peaks": pk, "sizes": tiralix_run(pk, args.batch, min(args.steps, 64), args.warmup)}))
         return 0
     if args.only == "issue-rate":
         # what the thread that issues tensor-core products costs: cycles per instruction, one or two issuing threads

@@ -125,11 +125,41 @@ __global__ void head_gate_kernel(const TA* __restrict__ att, const float* __rest
     }
 }
 
+// The same by fours (head sizes and row distances that are multiples of four, aligned pointers): one sigmoid per four values.
+template <typename TA>
+__global__ void head_gate4_kernel(const TA* __restrict__ att, const float* __restrict__ p, int ldp, int g_off, TA* __restrict__ out,
+                                  int ldo, int H, int hdv, size_t total4, float mult) {
+    ik_pdl_wait();
+    IK_AFTER_WAIT(att);
+    IK_AFTER_WAIT(p);
+    ik_pdl_launch_dependents();
+    const size_t stride = (size_t)gridDim.x * blockDim.x;
+    const int cols4 = H * hdv / 4;
+    for (size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x; idx < total4; idx += stride) {
+        const size_t t = idx / cols4;
+        const int c = (int)(idx - t * cols4) * 4, h = c / hdv;
+        const float g = (p ? 1.0f / (1.0f + expf(-p[t * ldp + g_off + h])) : 1.0f);
+        float4 v = ik_ld4(att, t * (size_t)(H * hdv) + c);
+        v.x = v.x * g * mult; v.y = v.y * g * mult; v.z = v.z * g * mult; v.w = v.w * g * mult;
+        ik_st4(out, t * ldo + c, v);
+    }
+}
+
 IK_EXPORT int ik_head_gate(const void* att, const float* p, int ldp, int g_off, void* out, int dtype, int ldo, int T, int H,
                            int hdv, float mult, cudaStream_t stream) {
     if (T < 0 || H <= 0 || hdv <= 0 || ldo < H * hdv) return IK_BAD_ARGUMENT;
     if (T == 0) return IK_OK;
     const size_t total = (size_t)T * H * hdv;
+    if (hdv % 4 == 0 && ldo % 4 == 0 && (uintptr_t)att % 16 == 0 && (uintptr_t)out % 16 == 0 && (dtype == IK_F32 || dtype == IK_BF16)) {
+        const size_t total4 = total / 4;
+        const int blocks4 = (int)((total4 + 255) / 256 < 65535 * 16 ? (total4 + 255) / 256 : 65535 * 16);
+        if (dtype == IK_F32)
+            IK_RETURN_IF_ERROR(ik_launch(head_gate4_kernel<float>, blocks4, 256, 0, stream, (const float*)att, p, ldp, g_off, (float*)out, ldo, H, hdv, total4, mult));
+        else
+            IK_RETURN_IF_ERROR(ik_launch(head_gate4_kernel<__nv_bfloat16>, blocks4, 256, 0, stream, (const __nv_bfloat16*)att, p, ldp, g_off,
+                                         (__nv_bfloat16*)out, ldo, H, hdv, total4, mult));
+        IK_LAUNCH_STATUS();
+    }
     const int blocks = (int)((total + 255) / 256 < 65535 * 16 ? (total + 255) / 256 : 65535 * 16);
     if (dtype == IK_F32)
         IK_RETURN_IF_ERROR(ik_launch(head_gate_kernel<float>, blocks, 256, 0, stream, (const float*)att, p, ldp, g_off, (float*)out, ldo, H, hdv, total, mult));

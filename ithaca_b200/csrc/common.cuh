@@ -41,6 +41,15 @@ __device__ __forceinline__ void ik_st4(__nv_bfloat16* p, size_t i, float4 v) {
     *reinterpret_cast<uint2*>(p + i) = w;
 }
 
+// Four consecutive values as floats (16-byte aligned float source, 8-byte aligned bfloat16 source).
+__device__ __forceinline__ float4 ik_ld4(const float* p, size_t i) { return *reinterpret_cast<const float4*>(p + i); }
+__device__ __forceinline__ float4 ik_ld4(const __nv_bfloat16* p, size_t i) {
+    const uint2 w = *reinterpret_cast<const uint2*>(p + i);
+    const __nv_bfloat162 lo = *reinterpret_cast<const __nv_bfloat162*>(&w.x), hi = *reinterpret_cast<const __nv_bfloat162*>(&w.y);
+    const float2 a = __bfloat1622float2(lo), b = __bfloat1622float2(hi);
+    return make_float4(a.x, a.y, b.x, b.y);
+}
+
 // silu(g) * u with silu(x) = x / (1 + exp(-x)).
 __device__ __forceinline__ float ik_swiglu(float g, float u) { return g / (1.0f + expf(-g)) * u; }
 // The same with the hardware's approximate exp and reciprocal (relative error ~1e-6), for results that are

@@ -186,9 +186,30 @@ __global__ void cast_kernel(const float* __restrict__ in, int ld_in, TO* __restr
     }
 }
 
+// The same by fours, for widths and row distances that are multiples of four and aligned pointers.
+template <typename TO>
+__global__ void cast4_kernel(const float* __restrict__ in, int ld_in, TO* __restrict__ out, int ld_out, int cols4, size_t total4) {
+    ik_pdl_wait();
+    IK_AFTER_WAIT(in);
+    ik_pdl_launch_dependents();
+    const size_t stride = (size_t)gridDim.x * blockDim.x;
+    for (size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x; idx < total4; idx += stride) {
+        const size_t r = idx / cols4, c = (idx - r * cols4) * 4;
+        ik_st4(out, r * ld_out + c, ik_ld4(in, r * ld_in + c));
+    }
+}
+
 IK_EXPORT int ik_cast(const float* in, int ld_in, void* out, int out_dtype, int ld_out, int rows, int cols, cudaStream_t stream) {
     if (rows < 0 || cols <= 0 || ld_in < cols || ld_out < cols) return IK_BAD_ARGUMENT;
     if (rows == 0) return IK_OK;
+    if (cols % 4 == 0 && ld_in % 4 == 0 && ld_out % 4 == 0 && (uintptr_t)in % 16 == 0 && (uintptr_t)out % 16 == 0 &&
+        (out_dtype == IK_F32 || out_dtype == IK_BF16)) {
+        const size_t total4 = (size_t)rows * (cols / 4);
+        const int blocks4 = (int)((total4 + 255) / 256 < 65535 * 16 ? (total4 + 255) / 256 : 65535 * 16);
+        if (out_dtype == IK_F32) IK_RETURN_IF_ERROR(ik_launch(cast4_kernel<float>, blocks4, 256, 0, stream, in, ld_in, (float*)out, ld_out, cols / 4, total4));
+        else IK_RETURN_IF_ERROR(ik_launch(cast4_kernel<__nv_bfloat16>, blocks4, 256, 0, stream, in, ld_in, (__nv_bfloat16*)out, ld_out, cols / 4, total4));
+        IK_LAUNCH_STATUS();
+    }
     const size_t total = (size_t)rows * cols;
     const int blocks = (int)((total + 255) / 256 < 65535 * 16 ? (total + 255) / 256 : 65535 * 16);
     if (out_dtype == IK_F32) IK_RETURN_IF_ERROR(ik_launch(cast_kernel<float>, blocks, 256, 0, stream, in, ld_in, (float*)out, ld_out, cols, total));

@@ -1028,9 +1028,10 @@ def selective_scan(u: torch.Tensor, dt_raw: torch.Tensor, dt_bias: Optional[torc
 
 
 def decay_attention(p: torch.Tensor, q_off: int, k_off: int, v_off: int, decay: torch.Tensor, state: torch.Tensor, ctx,
-                    n_heads: int, dk: int, dv: int, act: bool = True) -> torch.Tensor:
+                    n_heads: int, dk: int, dv: int, act: int = 1) -> torch.Tensor:
     """Linear attention with one constant decay per head: S <- a S + k v^T, o = S^T q, over the step's tokens.  q, k, v
-    are column ranges of ``p`` (float), passed through silu when ``act``.  ``state`` [max_slots, 2, heads, dk, dv] float.
+    are column ranges of ``p`` (float), passed through silu when ``act`` (2: silu with the hardware's approximate
+    exponential and reciprocal, for the 16-bit path).  ``state`` [max_slots, 2, heads, dk, dv] float.
     Returns float [T, heads * dv]."""
     _need(p, "p", torch.float32, contiguous=False)
     _need(decay, "decay", torch.float32)
@@ -1044,7 +1045,7 @@ def decay_attention(p: torch.Tensor, q_off: int, k_off: int, v_off: int, decay: 
           4 * T * n_heads * dk * dv)
     _check(lib().ik_decay_attention(_ptr(p), p.stride(0), q_off, k_off, v_off, _ptr(decay), _ptr(state), _ptr(ctx.slots),
                                     _ptr(ctx.cu_seqlens), _ptr(ctx.kv_lens), _ptr(out), T, ctx.n_seqs, n_heads, dk, dv,
-                                    1 if act else 0, _stream()), "decay_attention")
+                                    int(act), _stream()), "decay_attention")
     return out
 
 

@@ -56,6 +56,38 @@ causal_conv_kernel(const float* __restrict__ x, int ldx, const float* __restrict
     ik_st(out, idx, act ? ik_silu(acc) : acc);
 }
 
+// The same for four neighbouring channels per thread (channel counts and row distances that are multiples of four,
+// aligned pointers): 16-byte accesses, and a token's few index computations once per four results.
+template <typename TO>
+__global__ void __launch_bounds__(256)
+causal_conv4_kernel(const float* __restrict__ x, int ldx, const float* __restrict__ w, const float* __restrict__ bias,
+                    float* __restrict__ ring, const int* __restrict__ slots, const int* __restrict__ cu_seqlens,
+                    const int* __restrict__ token_seq, const int* __restrict__ token_pos, TO* __restrict__ out,
+                    int T, int C, int taps, int act, int inline_ring) {
+    ik_pdl_wait();
+    IK_AFTER_WAIT(x);
+    IK_AFTER_WAIT(slots);
+    IK_AFTER_WAIT(cu_seqlens);
+    IK_AFTER_WAIT(token_seq);
+    IK_AFTER_WAIT(token_pos);
+    ik_pdl_launch_dependents();
+    const int c = (blockIdx.y * blockDim.x + threadIdx.x) * 4, t = blockIdx.x;
+    if (c >= C) return;
+    const int b = token_seq[t], pos = token_pos[t], first = cu_seqlens[b];
+    const float* rg = ring ? ring + (size_t)slots[b] * taps * C : nullptr;
+    float4 acc = bias ? ik_ld4(bias, c) : make_float4(0.f, 0.f, 0.f, 0.f);
+    for (int j = 0; j < taps; j++) {
+        const int back = taps - 1 - j;
+        if (back > pos) continue;
+        const float4 u = t - back >= first ? ik_ld4(x, (size_t)(t - back) * ldx + c) : ik_ld4(rg, (size_t)((pos - back) % taps) * C + c);
+        const float4 wj = ik_ld4(w, (size_t)j * C + c);
+        acc.x = fmaf(wj.x, u.x, acc.x); acc.y = fmaf(wj.y, u.y, acc.y); acc.z = fmaf(wj.z, u.z, acc.z); acc.w = fmaf(wj.w, u.w, acc.w);
+    }
+    if (inline_ring && ring) ik_st4(ring, ((size_t)slots[b] * taps + pos % taps) * C + c, ik_ld4(x, (size_t)t * ldx + c));
+    if (act) { acc.x = ik_silu(acc.x); acc.y = ik_silu(acc.y); acc.z = ik_silu(acc.z); acc.w = ik_silu(acc.w); }
+    ik_st4(out, (size_t)t * C + c, acc);
+}
+
 // The last `taps` inputs of every sequence go into its ring.
 __global__ void __launch_bounds__(256)
 conv_ring_kernel(const float* __restrict__ x, int ldx, float* __restrict__ ring, const int* __restrict__ slots,
@@ -85,7 +117,18 @@ IK_EXPORT int ik_causal_conv(const float* x, int ldx, const float* w, const floa
     const size_t total = (size_t)T * C;
     const int blocks = (int)((total + 255) / 256);
     const int inl = one_token_each && taps > 1;
-    if (out_dtype == IK_F32)
+    const bool by4 = C % 4 == 0 && ldx % 4 == 0 && (uintptr_t)x % 16 == 0 && (uintptr_t)w % 16 == 0 && (uintptr_t)out % 16 == 0 &&
+                     (!bias || (uintptr_t)bias % 16 == 0) && (!ring || (uintptr_t)ring % 16 == 0);
+    if (by4 && (out_dtype == IK_F32 || out_dtype == IK_BF16)) {
+        const int threads = C / 4 >= 256 ? 256 : ((C / 4 + 31) / 32) * 32;
+        const dim3 grid(T, (C / 4 + threads - 1) / threads);
+        if (out_dtype == IK_F32)
+            IK_RETURN_IF_ERROR(ik_launch(causal_conv4_kernel<float>, grid, threads, 0, stream, x, ldx, w, bias, ring, slots, cu_seqlens,
+                                         token_seq, token_pos, (float*)out, T, C, taps, act, inl));
+        else
+            IK_RETURN_IF_ERROR(ik_launch(causal_conv4_kernel<__nv_bfloat16>, grid, threads, 0, stream, x, ldx, w, bias, ring, slots,
+                                         cu_seqlens, token_seq, token_pos, (__nv_bfloat16*)out, T, C, taps, act, inl));
+    } else if (out_dtype == IK_F32)
         IK_RETURN_IF_ERROR(ik_launch(causal_conv_kernel<float>, blocks, 256, 0, stream, x, ldx, w, bias, ring, slots, cu_seqlens,
                                      token_seq, token_pos, (float*)out, T, C, taps, act, inl));
     else if (out_dtype == IK_BF16)
@@ -103,17 +146,26 @@ IK_EXPORT int ik_causal_conv(const float* x, int ldx, const float* w, const floa
 // ------------------------------------------------------------------ selective scan
 // Per channel c and state n:  S[c, n] <- exp(dt_c A[c, n]) S[c, n] + dt_c u_c B_n;  y_c = sum_n S[c, n] C_n + D_c u_c;
 // out = y * silu(z).  dt = softplus(dt_raw + dt_bias).  B_n, C_n are columns of `bc` (row stride ldbc), z of `z`
-// (row stride ldz).  L lanes share a channel: lane l holds states l, l + L, ...; their sums are added by shuffles in a
-// fixed order.  One block row per sequence, tokens in order.
-constexpr int SCAN_NPT = 8;        // states per thread
+// (row stride ldz).  L lanes (a power of two) share a channel: lane l holds states l, l + L, ... (NPT of them at most);
+// their sums are added by shuffles in a fixed order.  One block row per sequence, tokens in order.
+//
+// The tokens go through shared memory in tiles: while a tile is computed, the next tile's inputs are on their way
+// into registers; softplus and silu are applied when a tile is stored, by all threads at once, so that the
+// token-by-token chain holds only the exponential and the multiply-adds.  What is computed for a token does not
+// depend on where tiles begin.  FAST (16-bit inputs): exponentials and the gate's sigmoid are the hardware's
+// approximations.
+template <bool FAST> __device__ __forceinline__ float ik_silu_as(float x) {
+    return FAST ? x * __frcp_rn(1.0f + __expf(-x)) : x / (1.0f + expf(-x));
+}
 
-template <typename TU, typename TO>
+template <typename TU, typename TO, bool FAST, int NPT>
 __global__ void __launch_bounds__(128)
 selective_scan_kernel(const TU* __restrict__ u, const float* __restrict__ dt_raw, const float* __restrict__ dt_bias,
                       const float* __restrict__ A, const float* __restrict__ bc, int ldbc, int b_off, int c_off,
                       const float* __restrict__ Dv, const float* __restrict__ z, int ldz, float* __restrict__ state,
                       const int* __restrict__ slots, const int* __restrict__ cu_seqlens, const int* __restrict__ kv_lens,
-                      TO* __restrict__ out, int inner, int N, int L) {
+                      TO* __restrict__ out, int inner, int N, int L, int TT, int np2_shift) {
+    extern __shared__ __align__(16) float sm[];      // [2][TT][3 CH + NP2]: x, dt, silu(z) per channel; B then C (padded to NP2)
     ik_pdl_wait();
     IK_AFTER_WAIT(u);
     IK_AFTER_WAIT(dt_raw);
@@ -123,62 +175,100 @@ selective_scan_kernel(const TU* __restrict__ u, const float* __restrict__ dt_raw
     IK_AFTER_WAIT(cu_seqlens);
     IK_AFTER_WAIT(kv_lens);
     ik_pdl_launch_dependents();
-    const int b = blockIdx.y;
-    const int l = threadIdx.x & (L - 1);
-    const int c = blockIdx.x * (128 / L) + threadIdx.x / L;
+    const int b = blockIdx.y, CH = 128 / L, NP2 = 1 << np2_shift, W = 3 * CH + NP2;
+    const int chs = 31 - __clz(CH);
+    const int l = threadIdx.x & (L - 1), ch = threadIdx.x / L;
+    const int c0 = blockIdx.x * CH, c = c0 + ch;
     const bool live = c < inner;
     const int cc = live ? c : inner - 1;                     // idle lanes follow along (the shuffles need them)
     const int lo = cu_seqlens[b], hi = cu_seqlens[b + 1], end = kv_lens[b], start = end - (hi - lo);
+    if (hi <= lo) return;
     float* st_in = state + ((size_t)slots[b] * 2 + ((start - 1) & 1)) * inner * N + (size_t)cc * N;
     float* st_out = state + ((size_t)slots[b] * 2 + ((end - 1) & 1)) * inner * N + (size_t)cc * N;
-    float S[SCAN_NPT], a[SCAN_NPT];
+    float S[NPT], a[NPT];
     #pragma unroll
-    for (int r = 0; r < SCAN_NPT; r++) {
+    for (int r = 0; r < NPT; r++) {
         const int n = l + L * r;
         a[r] = n < N ? A[(size_t)cc * N + n] : 0.f;
         S[r] = (n < N && start > 0) ? st_in[n] : 0.f;
     }
-    const float bias = dt_bias ? dt_bias[cc] : 0.f, dskip = Dv ? Dv[cc] : 0.f;
-    // the next token's inputs are asked for while this one is computed
-    float xn = 0.f, dn = 0.f, zn = 0.f, Bn[SCAN_NPT], Cn[SCAN_NPT];
-    auto fetch = [&](int t) {
-        xn = ik_ld(u, (size_t)t * inner + cc);
-        dn = dt_raw[(size_t)t * inner + cc];
-        zn = z ? z[(size_t)t * ldz + cc] : 0.f;
-        const float* row = bc + (size_t)t * ldbc;
+    const float dskip = Dv ? Dv[cc] : 0.f;
+    const int per_tile = TT * W;
+    // staging: x, dt, z are TT x CH each (at most 512 elements: four per thread), B | C is TT x NP2 (at most 2048: sixteen)
+    float rx[4], rd[4], rz[4], rb[16];
+    auto fetch = [&](int t0) {
         #pragma unroll
-        for (int r = 0; r < SCAN_NPT; r++) {
-            const int n = l + L * r;
-            Bn[r] = n < N ? row[b_off + n] : 0.f;
-            Cn[r] = n < N ? row[c_off + n] : 0.f;
-        }
-    };
-    if (lo < hi) fetch(lo);
-    for (int t = lo; t < hi; t++) {
-        const float x = xn, zz = zn, dt = ik_softplus(dn + bias);
-        float Bt[SCAN_NPT], Ct[SCAN_NPT];
-        #pragma unroll
-        for (int r = 0; r < SCAN_NPT; r++) { Bt[r] = Bn[r]; Ct[r] = Cn[r]; }
-        if (t + 1 < hi) fetch(t + 1);
-        const float dx = dt * x;
-        float acc = 0.f;
-        #pragma unroll
-        for (int r = 0; r < SCAN_NPT; r++) {
-            if (l + L * r < N) {
-                S[r] = fmaf(expf(dt * a[r]), S[r], dx * Bt[r]);
-                acc = fmaf(S[r], Ct[r], acc);
+        for (int k = 0; k < 4; k++) {
+            const int e = threadIdx.x + k * 128, tt = e >> chs, col = c0 + (e & (CH - 1));
+            const int t = min(t0 + tt, hi - 1);
+            rx[k] = rd[k] = rz[k] = 0.f;
+            if (tt < TT && col < inner) {
+                rx[k] = ik_ld(u, (size_t)t * inner + col);
+                rd[k] = dt_raw[(size_t)t * inner + col] + (dt_bias ? dt_bias[col] : 0.f);
+                if (z) rz[k] = z[(size_t)t * ldz + col];
             }
         }
-        for (int o = L >> 1; o > 0; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
-        if (l == 0 && live) {
-            float y = fmaf(dskip, x, acc);
-            if (z) y *= ik_silu(zz);
-            ik_st(out, (size_t)t * inner + c, y);
-        }
-    }
-    if (live && hi > lo) {
         #pragma unroll
-        for (int r = 0; r < SCAN_NPT; r++) {
+        for (int k = 0; k < 16; k++) {
+            const int e = threadIdx.x + k * 128, tt = e >> np2_shift, n = e & (NP2 - 1);
+            const int t = min(t0 + tt, hi - 1);
+            rb[k] = 0.f;
+            if (tt < TT && n < 2 * N) rb[k] = n < N ? bc[(size_t)t * ldbc + b_off + n] : bc[(size_t)t * ldbc + c_off + n - N];
+        }
+    };
+    auto store = [&](int buf) {
+        float* tile = sm + buf * per_tile;
+        #pragma unroll
+        for (int k = 0; k < 4; k++) {
+            const int e = threadIdx.x + k * 128, tt = e >> chs, w = e & (CH - 1);
+            if (tt < TT) {
+                tile[tt * W + w] = rx[k];
+                tile[tt * W + CH + w] = ik_softplus(rd[k]);
+                tile[tt * W + 2 * CH + w] = ik_silu_as<FAST>(rz[k]);
+            }
+        }
+        #pragma unroll
+        for (int k = 0; k < 16; k++) {
+            const int e = threadIdx.x + k * 128, tt = e >> np2_shift, n = e & (NP2 - 1);
+            if (tt < TT) tile[tt * W + 3 * CH + n] = rb[k];
+        }
+    };
+    fetch(lo);
+    store(0);
+    __syncthreads();
+    int buf = 0;
+    for (int t0 = lo; t0 < hi; t0 += TT, buf ^= 1) {
+        if (t0 + TT < hi) fetch(t0 + TT);
+        const int n_here = min(TT, hi - t0);
+        for (int tt = 0; tt < n_here; tt++) {
+            const float* row = sm + buf * per_tile + tt * W;
+            const float x = row[ch], dt = row[CH + ch], gz = row[2 * CH + ch];
+            const float dx = dt * x;
+            float acc0 = 0.f, acc1 = 0.f;
+            #pragma unroll
+            for (int r = 0; r < NPT; r++) {
+                const int n = l + L * r;
+                if (n < N) {
+                    const float da = FAST ? __expf(dt * a[r]) : expf(dt * a[r]);
+                    S[r] = fmaf(da, S[r], dx * row[3 * CH + n]);
+                    if (r & 1) acc1 = fmaf(S[r], row[3 * CH + N + n], acc1);
+                    else acc0 = fmaf(S[r], row[3 * CH + N + n], acc0);
+                }
+            }
+            float acc = acc0 + acc1;
+            for (int o = L >> 1; o > 0; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
+            if (l == 0 && live) {
+                float y = fmaf(dskip, x, acc);
+                if (z) y *= gz;
+                ik_st(out, (size_t)(t0 + tt) * inner + c, y);
+            }
+        }
+        if (t0 + TT < hi) store(buf ^ 1);
+        __syncthreads();
+    }
+    if (live) {
+        #pragma unroll
+        for (int r = 0; r < NPT; r++) {
             const int n = l + L * r;
             if (n < N) st_out[n] = S[r];
         }
@@ -191,17 +281,34 @@ IK_EXPORT int ik_selective_scan(const void* u, int u_dtype, const float* dt_raw,
                                 int out_dtype, int T, int B, int inner, int N, cudaStream_t stream) {
     if (T < 0 || B < 0 || inner <= 0 || N <= 0 || !state || b_off < 0 || c_off < 0 || ldbc < N) return IK_BAD_ARGUMENT;
     if (T == 0 || B == 0) return IK_OK;
+    // two states a thread while a warp's lanes suffice for a channel (many short chains fill the SMs), else eight
+    const int npt = N <= 64 ? 2 : 8;
     int L = 1;
-    while (L * SCAN_NPT < N) L *= 2;
+    while (L * npt < N) L *= 2;
     if (L > 32) return IK_UNSUPPORTED;
-    const dim3 grid((inner + 128 / L - 1) / (128 / L), B);
-#define IK_SCAN(TU, TO)                                                                                                    \
-    IK_RETURN_IF_ERROR(ik_launch(selective_scan_kernel<TU, TO>, grid, 128, 0, stream, (const TU*)u, dt_raw, dt_bias, A, bc, ldbc, \
-                                 b_off, c_off, Dv, z, ldz, state, slots, cu_seqlens, kv_lens, (TO*)out, inner, N, L))
-    if (u_dtype == IK_F32 && out_dtype == IK_F32) IK_SCAN(float, float);
-    else if (u_dtype == IK_BF16 && out_dtype == IK_BF16) IK_SCAN(__nv_bfloat16, __nv_bfloat16);
-    else if (u_dtype == IK_F32 && out_dtype == IK_BF16) IK_SCAN(float, __nv_bfloat16);
-    else if (u_dtype == IK_BF16 && out_dtype == IK_F32) IK_SCAN(__nv_bfloat16, float);
+    const int CH = 128 / L;
+    int shift = 0;
+    while ((1 << shift) < 2 * N) shift++;
+    int TT = 16;
+    if (TT > 512 / CH) TT = 512 / CH;
+    if (TT > (2048 >> shift)) TT = 2048 >> shift;
+    if (TT < 1) return IK_UNSUPPORTED;
+    const int W = 3 * CH + (1 << shift);
+    const dim3 grid((inner + CH - 1) / CH, B);
+    const size_t smem = (size_t)2 * TT * W * sizeof(float);
+#define IK_SCAN(TU, TO, FAST)                                                                                               \
+    do {                                                                                                                    \
+        if (npt == 2)                                                                                                       \
+            IK_RETURN_IF_ERROR(ik_launch(selective_scan_kernel<TU, TO, FAST, 2>, grid, 128, smem, stream, (const TU*)u, dt_raw, dt_bias, A, bc, \
+                                         ldbc, b_off, c_off, Dv, z, ldz, state, slots, cu_seqlens, kv_lens, (TO*)out, inner, N, L, TT, shift)); \
+        else                                                                                                                \
+            IK_RETURN_IF_ERROR(ik_launch(selective_scan_kernel<TU, TO, FAST, 8>, grid, 128, smem, stream, (const TU*)u, dt_raw, dt_bias, A, bc, \
+                                         ldbc, b_off, c_off, Dv, z, ldz, state, slots, cu_seqlens, kv_lens, (TO*)out, inner, N, L, TT, shift)); \
+    } while (0)
+    if (u_dtype == IK_F32 && out_dtype == IK_F32) IK_SCAN(float, float, false);
+    else if (u_dtype == IK_BF16 && out_dtype == IK_BF16) IK_SCAN(__nv_bfloat16, __nv_bfloat16, true);
+    else if (u_dtype == IK_F32 && out_dtype == IK_BF16) IK_SCAN(float, __nv_bfloat16, false);
+    else if (u_dtype == IK_BF16 && out_dtype == IK_F32) IK_SCAN(__nv_bfloat16, float, true);
     else return IK_BAD_ARGUMENT;
 #undef IK_SCAN
     IK_LAUNCH_STATUS();
@@ -209,17 +316,23 @@ IK_EXPORT int ik_selective_scan(const void* u, int u_dtype, const float* dt_raw,
 
 // ------------------------------------------------------------------ linear attention with a constant decay per head
 // Per head h with decay a_h:  S <- a_h S + k v^T (S is dk x dv);  o = S^T q.  q, k, v are columns of the projections'
-// output `p` (row stride ldp), each passed through silu when act is set.  A block holds 32 columns of one head's S for
-// one sequence: thread (j, part) keeps rows part*R .. part*R + R - 1 of column j in registers.  q and k of a token are
-// staged in shared memory (two buffers: the next token's are fetched while this one is computed); the parts' sums
-// of a column are added in part order.
-constexpr int LA_RMAX = 32;
+// output `p` (row stride ldp), each passed through silu when act is set (act 2: with the hardware's approximate
+// exponential and reciprocal, for the 16-bit path).  A block holds 32 columns of one head's S for one sequence: thread
+// (j, part) keeps rows part*R .. part*R + R - 1 of column j in registers, one warp per part, up to 16 of them.  The
+// tokens go through shared memory in tiles (q, k and the block's 32 columns of v, activation applied when a tile is
+// stored); while a tile is computed the next one is on its way into registers, every warp fetching whole token rows.
+// The parts' sums of a column are added in part order, once per tile.  What is computed for a token does not depend on
+// where tiles begin.  FULL: dk = parts * RMAX and RMAX is a multiple of 4: no row is guarded and q, k come from shared
+// memory four at a time.
+constexpr int LA_ROWS = 2;         // token rows a warp stages per tile, at most
+constexpr int LA_PER_ROW = 17;     // 32-wide pieces of a staged row, at most: 2 dk + 32 <= 544
 
-__global__ void __launch_bounds__(256)
+template <int RMAX, bool FULL>
+__global__ void __launch_bounds__(512)
 decay_attention_kernel(const float* __restrict__ p, int ldp, int q_off, int k_off, int v_off, const float* __restrict__ decay,
                        float* __restrict__ state, const int* __restrict__ slots, const int* __restrict__ cu_seqlens,
-                       const int* __restrict__ kv_lens, float* __restrict__ out, int H, int dk, int dv, int R, int act) {
-    extern __shared__ __align__(16) float sm[];          // [2][2 dk] q then k;  [2][parts][32] partial sums
+                       const int* __restrict__ kv_lens, float* __restrict__ out, int H, int dk, int dv, int R, int act, int TT) {
+    extern __shared__ __align__(16) float sm[];          // [2][TT][2 dk + 32]: q, k, v;  [2][TT][parts][32] partial sums
     ik_pdl_wait();
     IK_AFTER_WAIT(p);
     IK_AFTER_WAIT(slots);
@@ -227,63 +340,104 @@ decay_attention_kernel(const float* __restrict__ p, int ldp, int q_off, int k_of
     IK_AFTER_WAIT(kv_lens);
     ik_pdl_launch_dependents();
     const int b = blockIdx.x, h = blockIdx.y, j = threadIdx.x, part = threadIdx.y, parts = blockDim.y;
-    const int col = blockIdx.z * 32 + j;
+    const int col0 = blockIdx.z * 32, col = col0 + j;
     const bool live = col < dv;
     const int ccol = live ? col : dv - 1;
-    const int tid = part * 32 + j, nthreads = parts * 32;
-    float* qk = sm;
-    float* partial = sm + 4 * dk;
+    const int tid = part * 32 + j, nthreads = parts * 32, W = 2 * dk + 32, per_tile = TT * W;
+    float* partial = sm + 2 * per_tile;
     const int lo = cu_seqlens[b], hi = cu_seqlens[b + 1], end = kv_lens[b], start = end - (hi - lo);
     if (hi <= lo) return;
     const float a = decay[h];
     const size_t per = (size_t)H * dk * dv;
     const float* st_in = state + ((size_t)slots[b] * 2 + ((start - 1) & 1)) * per + (size_t)h * dk * dv;
     float* st_out = state + ((size_t)slots[b] * 2 + ((end - 1) & 1)) * per + (size_t)h * dk * dv;
-    float S[LA_RMAX];
+    float S[RMAX];
     #pragma unroll
-    for (int r = 0; r < LA_RMAX; r++) {
+    for (int r = 0; r < RMAX; r++) {
         const int i = part * R + r;
         S[r] = (r < R && i < dk && start > 0) ? st_in[(size_t)i * dv + ccol] : 0.f;
     }
-    // staging: element e < dk is q_e, dk <= e < 2 dk is k_(e - dk)
-    auto stage = [&](int t, int buf) {
-        const float* row = p + (size_t)t * ldp;
-        for (int e = tid; e < 2 * dk; e += nthreads) {
-            float v = e < dk ? row[q_off + h * dk + e] : row[k_off + h * dk + e - dk];
-            qk[buf * 2 * dk + e] = act ? ik_silu(v) : v;
-        }
-    };
-    stage(lo, 0);
-    float vn = p[(size_t)lo * ldp + v_off + h * dv + ccol];
-    __syncthreads();
-    for (int t = lo; t < hi; t++) {
-        const int buf = (t - lo) & 1;
-        const float v = act ? ik_silu(vn) : vn;
-        if (t + 1 < hi) {
-            vn = p[(size_t)(t + 1) * ldp + v_off + h * dv + ccol];
-            stage(t + 1, buf ^ 1);
-        }
-        const float* q = qk + buf * 2 * dk + part * R;
-        const float* k = q + dk;
-        float acc = 0.f;
+    // staging: warp `part` fetches token rows part, part + parts, ...; lane j the columns j, j + 32, ... of a row
+    float regs[LA_ROWS][LA_PER_ROW];
+    auto fetch = [&](int t0) {
         #pragma unroll
-        for (int r = 0; r < LA_RMAX; r++) {
-            if (r < R && part * R + r < dk) {
-                S[r] = fmaf(a, S[r], k[r] * v);
-                acc = fmaf(S[r], q[r], acc);
+        for (int rr = 0; rr < LA_ROWS; rr++) {
+            const int tt = part + parts * rr;
+            const float* row = p + (size_t)min(t0 + tt, hi - 1) * ldp;
+            #pragma unroll
+            for (int kk = 0; kk < LA_PER_ROW; kk++) {
+                const int w = j + 32 * kk;
+                regs[rr][kk] = 0.f;
+                if (tt >= TT || w >= W) continue;
+                if (w < dk) regs[rr][kk] = row[q_off + h * dk + w];
+                else if (w < 2 * dk) regs[rr][kk] = row[k_off + h * dk + w - dk];
+                else if (col0 + w - 2 * dk < dv) regs[rr][kk] = row[v_off + h * dv + col0 + w - 2 * dk];
             }
         }
-        if (parts > 1) partial[(buf * parts + part) * 32 + j] = acc;
+    };
+    auto store = [&](int buf) {
+        #pragma unroll
+        for (int rr = 0; rr < LA_ROWS; rr++) {
+            const int tt = part + parts * rr;
+            #pragma unroll
+            for (int kk = 0; kk < LA_PER_ROW; kk++) {
+                const int w = j + 32 * kk;
+                if (tt >= TT || w >= W) continue;
+                const float x = regs[rr][kk];
+                sm[buf * per_tile + tt * W + w] = act == 2 ? ik_silu_as<true>(x) : act ? ik_silu_as<false>(x) : x;
+            }
+        }
+    };
+    fetch(lo);
+    store(0);
+    __syncthreads();
+    int buf = 0;
+    for (int t0 = lo; t0 < hi; t0 += TT, buf ^= 1) {
+        if (t0 + TT < hi) fetch(t0 + TT);
+        const int n_here = min(TT, hi - t0);
+        for (int tt = 0; tt < n_here; tt++) {
+            const float* q = sm + buf * per_tile + tt * W + part * R;
+            const float* k = q + dk;
+            const float v = sm[buf * per_tile + tt * W + 2 * dk + j];
+            float acc0 = 0.f, acc1 = 0.f;
+            if (FULL) {
+                #pragma unroll
+                for (int r = 0; r < RMAX; r += 4) {
+                    const float4 kk = *reinterpret_cast<const float4*>(k + r), qq = *reinterpret_cast<const float4*>(q + r);
+                    S[r] = fmaf(a, S[r], kk.x * v);         acc0 = fmaf(S[r], qq.x, acc0);
+                    S[r + 1] = fmaf(a, S[r + 1], kk.y * v); acc1 = fmaf(S[r + 1], qq.y, acc1);
+                    S[r + 2] = fmaf(a, S[r + 2], kk.z * v); acc0 = fmaf(S[r + 2], qq.z, acc0);
+                    S[r + 3] = fmaf(a, S[r + 3], kk.w * v); acc1 = fmaf(S[r + 3], qq.w, acc1);
+                }
+            } else {
+                #pragma unroll
+                for (int r = 0; r < RMAX; r++) {
+                    if (r < R && part * R + r < dk) {
+                        S[r] = fmaf(a, S[r], k[r] * v);
+                        if (r & 1) acc1 = fmaf(S[r], q[r], acc1);
+                        else acc0 = fmaf(S[r], q[r], acc0);
+                    }
+                }
+            }
+            const float acc = acc0 + acc1;
+            if (parts > 1) partial[((buf * TT + tt) * parts + part) * 32 + j] = acc;
+            else if (live) out[(size_t)(t0 + tt) * H * dv + h * dv + col] = acc;
+        }
+        if (t0 + TT < hi) store(buf ^ 1);
         __syncthreads();
-        if (part == 0 && live) {
-            float o = acc;
-            for (int pp = 1; pp < parts; pp++) o += partial[(buf * parts + pp) * 32 + j];
-            out[(size_t)t * H * dv + h * dv + col] = o;
+        if (parts > 1) {
+            for (int e = tid; e < n_here * 32; e += nthreads) {
+                const int tt = e >> 5, jj = e & 31;
+                if (col0 + jj >= dv) continue;
+                float o = 0.f;
+                for (int pp = 0; pp < parts; pp++) o += partial[((buf * TT + tt) * parts + pp) * 32 + jj];
+                out[(size_t)(t0 + tt) * H * dv + h * dv + col0 + jj] = o;
+            }
         }
     }
     if (live) {
         #pragma unroll
-        for (int r = 0; r < LA_RMAX; r++) {
+        for (int r = 0; r < RMAX; r++) {
             const int i = part * R + r;
             if (r < R && i < dk) st_out[(size_t)i * dv + col] = S[r];
         }
@@ -295,12 +449,30 @@ IK_EXPORT int ik_decay_attention(const float* p, int ldp, int q_off, int k_off, 
                                  int dk, int dv, int act, cudaStream_t stream) {
     if (T < 0 || B < 0 || H <= 0 || dk <= 0 || dv <= 0 || !state || !decay) return IK_BAD_ARGUMENT;
     if (T == 0 || B == 0) return IK_OK;
-    const int parts = (dk + LA_RMAX - 1) / LA_RMAX;
-    if (parts > 8) return IK_UNSUPPORTED;
-    const int R = (dk + parts - 1) / parts;
+    if (dk > 256) return IK_UNSUPPORTED;
+    int parts = (dk + 7) / 8;                       // eight rows a thread ...
+    if (parts > 16) parts = 16;                     // ... sixteen from 129 rows on
+    const int R = (dk + parts - 1) / parts, W = 2 * dk + 32;
+    int TT = LA_ROWS * parts;
+    if (TT > 16) TT = 16;
+    const bool full = dk == parts * R && (R == 8 || R == 16) && ldp % 4 == 0;
     const dim3 grid(B, H, (dv + 31) / 32), block(32, parts);
-    const size_t smem = (size_t)(4 * dk + 2 * parts * 32) * sizeof(float);
-    IK_RETURN_IF_ERROR(ik_launch(decay_attention_kernel, grid, block, smem, stream, p, ldp, q_off, k_off, v_off, decay, state, slots,
-                                 cu_seqlens, kv_lens, out, H, dk, dv, R, act));
+    const size_t smem = (size_t)(2 * TT * W + 2 * TT * parts * 32) * sizeof(float);
+    if (smem > 160 * 1024) return IK_UNSUPPORTED;
+#define IK_LA(RMAX, FULL)                                                                                                        \
+    do {                                                                                                                         \
+        static bool raised = false;                                                                                              \
+        if (smem > 48 * 1024 && !raised) {                                                                                       \
+            IK_RETURN_IF_ERROR(cudaFuncSetAttribute(decay_attention_kernel<RMAX, FULL>, cudaFuncAttributeMaxDynamicSharedMemorySize, 160 * 1024)); \
+            raised = true;                                                                                                       \
+        }                                                                                                                        \
+        IK_RETURN_IF_ERROR(ik_launch(decay_attention_kernel<RMAX, FULL>, grid, block, smem, stream, p, ldp, q_off, k_off, v_off, decay, state, \
+                                     slots, cu_seqlens, kv_lens, out, H, dk, dv, R, act, TT));                                    \
+    } while (0)
+    if (full && R == 8) IK_LA(8, true);
+    else if (full) IK_LA(16, true);
+    else if (R <= 8) IK_LA(8, false);
+    else IK_LA(16, false);
+#undef IK_LA
     IK_LAUNCH_STATUS();
 }

@@ -53,7 +53,8 @@ class DecayAttention:
         act = spec.get("activation", "silu")
         if act not in ("silu", "none"):
             raise ValueError(f"decay_attention: activation {act!r} is not supported (silu, none)")
-        self.act = act == "silu"
+        # 0 none, 1 silu, 2 silu with the hardware's approximate exponential (what feeds 16-bit products anyway)
+        self.act = 0 if act == "none" else 2 if runtime.dtype == "bfloat16" else 1
         self.gate = bool(spec.get("gate"))
         self.norm_eps = float(spec["norm_eps"])
         self.decay = torch.tensor(decay, dtype=torch.float32, device=runtime.device)
