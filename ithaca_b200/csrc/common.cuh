@@ -67,6 +67,21 @@ __device__ __forceinline__ float ik_glu_fast(float g, float u, float alpha, floa
     return g * __frcp_rn(1.0f + __expf(-alpha * g)) * (u + shift);
 }
 
+// How a product's epilogue joins the gate and up halves of its rows: kind 0 = not at all, 1 = silu(g) * u, 2 = the gate
+// with parameters above.  It converts from and to the plain flag, so code that only asks "is there a join" reads as before.
+struct IkGlu {
+    int kind;
+    float alpha, limit, shift;
+    __host__ __device__ IkGlu(int k = 0, float a = 1.f, float l = 0.f, float s = 0.f) : kind(k), alpha(a), limit(l), shift(s) {}
+    __host__ __device__ operator int() const { return kind; }
+};
+__device__ __forceinline__ float ik_glu_join(const IkGlu& j, float g, float u) {
+    return j.kind == 2 ? ik_glu(g, u, j.alpha, j.limit, j.shift) : ik_swiglu(g, u);
+}
+__device__ __forceinline__ float ik_glu_join_fast(const IkGlu& j, float g, float u) {
+    return j.kind == 2 ? ik_glu_fast(g, u, j.alpha, j.limit, j.shift) : ik_swiglu_fast(g, u);
+}
+
 // Value a float would have after a round trip through the storage type.
 template <typename T> __device__ __forceinline__ float ik_round_to(float v);
 template <> __device__ __forceinline__ float ik_round_to<float>(float v) { return v; }

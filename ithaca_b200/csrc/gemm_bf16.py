@@ -48,14 +48,14 @@ def gemm_swiglu(x: torch.Tensor, w_interleaved: torch.Tensor, out_dtype: torch.d
     g * sigmoid(alpha g) * (u + shift) with g and u clamped by ``limit``; None = silu(g) * u."""
     M, ff = x.shape[0], w_interleaved.shape[0] // 2
     out = torch.empty((M, ff), dtype=out_dtype, device=x.device)
-    if glu is not None:
-        gu = gemm(x, w_interleaved, out_dtype=torch.float32)
-        return ops.glu_act(gu, out_dtype, *glu, out=out, interleaved=True)
     if takes_skinny(M, w_interleaved.shape[0], w_interleaved.shape[1]):
-        done = ops.gemm_bf16_mma(x, w_interleaved, out=out, kind=1, swiglu=True)
+        done = ops.gemm_bf16_mma(x, w_interleaved, out=out, kind=1, swiglu=True, glu=glu)
     else:
-        done = ops.gemm_tcgen05(x, w_interleaved, out=out, status=ops.device_status(x.device), swiglu=True)
+        done = ops.gemm_tcgen05(x, w_interleaved, out=out, status=ops.device_status(x.device), swiglu=True, glu=glu)
     if done is None:
         gu = ops.gemm_simt(x, w_interleaved, out_dtype=torch.float32)
-        ops.swiglu(gu, out_dtype, out=out, interleaved=True)
+        if glu is None:
+            ops.swiglu(gu, out_dtype, out=out, interleaved=True)
+        else:
+            ops.glu_act(gu, out_dtype, *glu, out=out, interleaved=True)
     return out

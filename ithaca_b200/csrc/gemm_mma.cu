@@ -63,7 +63,7 @@ __device__ __forceinline__ void store_out(__nv_bfloat16* Y, size_t o, float v, i
 template <int NT, int U, typename TY, int R>
 __global__ void __launch_bounds__(256)
 gemm_skinny_kernel(const __nv_bfloat16* __restrict__ X, const __nv_bfloat16* __restrict__ W, TY* __restrict__ Y,
-                   int M, int N, int K, int ldx, int ldw, int ldy, int accumulate, int swiglu, const IkRopeStore rope) {
+                   int M, int N, int K, int ldx, int ldw, int ldy, int accumulate, IkGlu swiglu, const IkRopeStore rope) {
     constexpr int COLS = 8 * NT, H = R / 8;
     static_assert(R == 8 || R == 16, "a block owns 8 or 16 weight rows");
     extern __shared__ float red[];                       // [8 warps][R][COLS]
@@ -171,7 +171,7 @@ gemm_skinny_kernel(const __nv_bfloat16* __restrict__ X, const __nv_bfloat16* __r
                 gte += red[(size_t)w * R * COLS + (2 * pr) * COLS + m];
                 up += red[(size_t)w * R * COLS + (2 * pr + 1) * COLS + m];
             }
-            store_out(Y, (size_t)m * ldy + n0 / 2 + pr, ik_swiglu_fast(gte, up), 0);
+            store_out(Y, (size_t)m * ldy + n0 / 2 + pr, ik_glu_join_fast(swiglu, gte, up), 0);
         }
         return;
     }
@@ -187,7 +187,7 @@ gemm_skinny_kernel(const __nv_bfloat16* __restrict__ X, const __nv_bfloat16* __r
 
 template <int NT, int U, typename TY, int R = 16>
 int launch_skinny(const void* X, const void* W, void* Y, int M, int N, int K, int ldx, int ldw, int ldy,
-                  int accumulate, int swiglu, const IkRopeStore& rope, cudaStream_t stream) {
+                  int accumulate, IkGlu swiglu, const IkRopeStore& rope, cudaStream_t stream) {
     const size_t smem = (size_t)8 * R * 8 * NT * sizeof(float);
     auto kern = gemm_skinny_kernel<NT, U, TY, R>;
     IK_RETURN_IF_ERROR(ik_launch(kern, (N + R - 1) / R, 256, smem, stream, (const __nv_bfloat16*)X, (const __nv_bfloat16*)W,
@@ -318,7 +318,7 @@ bool aligned_ok(const void* X, const void* W, int K, int ldx, int ldw) {
 // kind: 0 = choose by M (skinny for M <= 64, else tiled), 1 = skinny, 2 = tiled.
 // swiglu (skinny only): W holds (gate j, up j) in rows (2j, 2j + 1); Y is [M, N / 2] = silu(gate) * up.
 static int gemm_bf16_mma_impl(const void* X, const void* W, void* Y, int y_dtype, int M, int N, int K, int ldx, int ldw,
-                              int ldy, int accumulate, int kind, int swiglu, const IkRopeStore& rope, cudaStream_t stream) {
+                              int ldy, int accumulate, int kind, IkGlu swiglu, const IkRopeStore& rope, cudaStream_t stream) {
     if (M < 0 || N <= 0 || K <= 0 || ldx < K || ldw < K || (!rope.q_out && ldy < (swiglu ? N / 2 : N))) return IK_BAD_ARGUMENT;
     if (swiglu && ((N & 1) || accumulate || kind == 2 || (kind == 0 && M > 64))) return IK_BAD_ARGUMENT;
     if (y_dtype != IK_F32 && y_dtype != IK_BF16) return IK_BAD_ARGUMENT;
@@ -345,10 +345,13 @@ static int gemm_bf16_mma_impl(const void* X, const void* W, void* Y, int y_dtype
                              : launch_tiled<__nv_bfloat16>(X, W, Y, M, N, K, ldx, ldw, ldy, accumulate, stream);
 }
 
+// swiglu: 0 = none, 1 = silu(gate) * up, 2 = gate * sigmoid(alpha gate) * (up + shift) with gate and up limited (common.cuh).
 IK_EXPORT int ik_gemm_bf16_mma(const void* X, const void* W, void* Y, int y_dtype, int M, int N, int K, int ldx, int ldw,
-                               int ldy, int accumulate, int kind, int swiglu, cudaStream_t stream) {
+                               int ldy, int accumulate, int kind, int swiglu, float glu_alpha, float glu_limit, float glu_shift,
+                               cudaStream_t stream) {
     IkRopeStore none = {};
-    return gemm_bf16_mma_impl(X, W, Y, y_dtype, M, N, K, ldx, ldw, ldy, accumulate, kind, swiglu, none, stream);
+    return gemm_bf16_mma_impl(X, W, Y, y_dtype, M, N, K, ldx, ldw, ldy, accumulate, kind, IkGlu(swiglu, glu_alpha, glu_limit, glu_shift),
+                              none, stream);
 }
 
 // The fused q/k/v product of up to 64 tokens with the rotary / cache epilogue (rope_store.cuh).  N must be

@@ -230,7 +230,7 @@ template <int BN, typename TY, int MODE>
 __global__ void __launch_bounds__(THREADS, 1)
 gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_x,
                     TY* __restrict__ Y, float* __restrict__ partial, int M, int N, int K, int ldy, int accumulate,
-                    int swiglu, int kb_per_split, int n_splits, int stream_k, int* status, const IkRopeStore rope, int bn,
+                    IkGlu swiglu, int kb_per_split, int n_splits, int stream_k, int* status, const IkRopeStore rope, int bn,
                     const int* tile_group) {
     // tile_group != nullptr: a grouped product.  W stacks several [N, K] matrices; token tile mt multiplies matrix
     // tile_group[mt] (rows group * N ... of W), and token tiles marked -1 are passed over.
@@ -606,7 +606,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
                             const float other = __shfl_xor_sync(0xffffffffu, odd ? v[c] : v[c + 8], 1);
                             const float gte = odd ? other : v[c], up = odd ? v[c + 8] : other;
                             const int m = m0 + c0 + c + (odd ? 8 : 0);
-                            if (feature < N && m < M) ik_st(Y, (size_t)m * ldy + (feature >> 1), ik_swiglu_fast(gte, up));
+                            if (feature < N && m < M) ik_st(Y, (size_t)m * ldy + (feature >> 1), ik_glu_join_fast(swiglu, gte, up));
                         }
                     } else {
                         if (accumulate) {
@@ -644,7 +644,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
 // Adds the K slices in slice order and writes Y.
 template <typename TY>
 __global__ void splitk_reduce_kernel(const float* __restrict__ partial, TY* __restrict__ Y, int M, int N, int ldy,
-                                     int splits, int accumulate, int swiglu, const IkRopeStore rope) {
+                                     int splits, int accumulate, IkGlu swiglu, const IkRopeStore rope) {
     ik_pdl_wait();
     ik_pdl_launch_dependents();
     asm volatile("" : "+l"(partial));      // the slices are the kernel before's results: no read of them may move above the wait
@@ -671,7 +671,7 @@ __global__ void splitk_reduce_kernel(const float* __restrict__ partial, TY* __re
                 g += partial[(size_t)z * total + m * N + 2 * j];
                 u += partial[(size_t)z * total + m * N + 2 * j + 1];
             }
-            ik_st(Y, m * ldy + j, ik_swiglu(g, u));
+            ik_st(Y, m * ldy + j, ik_glu_join(swiglu, g, u));
         }
         return;
     }
@@ -688,7 +688,7 @@ __global__ void splitk_reduce_kernel(const float* __restrict__ partial, TY* __re
 // Cluster mode: n_cl blocks per tile, each a slice of K, summed in rank 0's shared memory.
 template <int BN, typename TY>
 int launch_cluster(const CUtensorMap& mw, const CUtensorMap& mx, void* Y, int M, int N, int K, int ldy, int accumulate,
-                   int swiglu, int n_cl, int* status, const IkRopeStore& rope, int bn, cudaStream_t stream) {
+                   IkGlu swiglu, int n_cl, int* status, const IkRopeStore& rope, int bn, cudaStream_t stream) {
     typedef Cfg<BN> C;
     const int* groups = nullptr;
     if (C::RED_SLOTS == 0) return IK_UNSUPPORTED;
@@ -718,7 +718,7 @@ int launch_cluster(const CUtensorMap& mw, const CUtensorMap& mx, void* Y, int M,
 
 template <int BN, typename TY>
 int launch(const CUtensorMap& mw, const CUtensorMap& mx, void* Y, float* partial, int M, int N, int K, int ldy,
-           int accumulate, int swiglu, int splits, int* status, const IkRopeStore& rope, int bn, cudaStream_t stream,
+           int accumulate, IkGlu swiglu, int splits, int* status, const IkRopeStore& rope, int bn, cudaStream_t stream,
            const int* groups = nullptr) {
     typedef Cfg<BN> C;
     if (groups && splits != 1) return IK_BAD_ARGUMENT;
@@ -793,7 +793,7 @@ IK_EXPORT int ik_gemm_tcgen05_tile_width(int M, int N) {
 namespace {
 template <typename TY>
 int launch_pairs(const CUtensorMap& mw, const CUtensorMap& mx_half, void* Y, int M, int N, int K, int ldy, int accumulate,
-                 int swiglu, int* status, const IkRopeStore& rope, int bn, cudaStream_t stream) {
+                 IkGlu swiglu, int* status, const IkRopeStore& rope, int bn, cudaStream_t stream) {
     typedef Cfg<256> C;
     const int* groups = nullptr;
     auto kern = gemm_tcgen05_kernel<256, TY, 2>;
@@ -821,7 +821,7 @@ int launch_pairs(const CUtensorMap& mw, const CUtensorMap& mx_half, void* Y, int
 }
 
 int pairs_impl(const void* X, const void* W, void* Y, int y_dtype, int M, int N, int K, int ldx, int ldw, int ldy,
-               int accumulate, int swiglu, int* status, const IkRopeStore& rope, cudaStream_t stream) {
+               int accumulate, IkGlu swiglu, int* status, const IkRopeStore& rope, cudaStream_t stream) {
     if (M < 0 || N <= 0 || K <= 0 || ldx < K || ldw < K || (!rope.q_out && ldy < (swiglu ? N / 2 : N))) return IK_BAD_ARGUMENT;
     if (swiglu && ((N & 1) || accumulate)) return IK_BAD_ARGUMENT;
     if (y_dtype != IK_F32 && y_dtype != IK_BF16) return IK_BAD_ARGUMENT;
@@ -841,9 +841,11 @@ int pairs_impl(const void* X, const void* W, void* Y, int y_dtype, int M, int N,
 
 // Arguments as ik_gemm_tcgen05 without the scratch and the way of sharing out; IK_UNSUPPORTED up to 256 tokens.
 IK_EXPORT int ik_gemm_tcgen05_pairs(const void* X, const void* W, void* Y, int y_dtype, int M, int N, int K, int ldx, int ldw,
-                                    int ldy, int accumulate, int swiglu, int* status, cudaStream_t stream) {
+                                    int ldy, int accumulate, int swiglu, float glu_alpha, float glu_limit, float glu_shift,
+                                    int* status, cudaStream_t stream) {
     IkRopeStore none = {};
-    return pairs_impl(X, W, Y, y_dtype, M, N, K, ldx, ldw, ldy, accumulate, swiglu, status, none, stream);
+    return pairs_impl(X, W, Y, y_dtype, M, N, K, ldx, ldw, ldy, accumulate, IkGlu(swiglu, glu_alpha, glu_limit, glu_shift), status, none,
+                      stream);
 }
 
 IK_EXPORT int ik_gemm_qkv_rope_tcgen05_pairs(const void* X, const void* W, int M, int N, int K, int ldx, int ldw, int* status,
@@ -862,7 +864,7 @@ IK_EXPORT int ik_gemm_tcgen05_stream_k_bytes() { return (int)stream_k_bytes(); }
 // status: device int; set to 4 if a block gave up waiting (the result is then not to be used).
 // swiglu: W holds (gate j, up j) in rows (2j, 2j + 1); Y is [M, N / 2] = silu(gate) * up.
 static int gemm_tcgen05_impl(const void* X, const void* W, void* Y, int y_dtype, float* partial, int M, int N, int K,
-                             int ldx, int ldw, int ldy, int accumulate, int swiglu, int splits, int* status,
+                             int ldx, int ldw, int ldy, int accumulate, IkGlu swiglu, int splits, int* status,
                              const IkRopeStore& rope, cudaStream_t stream, const int* groups = nullptr, int n_groups = 1,
                              int bn_given = 0) {
     if (M < 0 || N <= 0 || K <= 0 || ldx < K || ldw < K || (!rope.q_out && ldy < (swiglu ? N / 2 : N)))
@@ -893,10 +895,11 @@ static int gemm_tcgen05_impl(const void* X, const void* W, void* Y, int y_dtype,
 }
 
 IK_EXPORT int ik_gemm_tcgen05(const void* X, const void* W, void* Y, int y_dtype, float* partial, int M, int N, int K,
-                              int ldx, int ldw, int ldy, int accumulate, int swiglu, int splits, int* status,
-                              cudaStream_t stream) {
+                              int ldx, int ldw, int ldy, int accumulate, int swiglu, float glu_alpha, float glu_limit, float glu_shift,
+                              int splits, int* status, cudaStream_t stream) {
     IkRopeStore none = {};
-    return gemm_tcgen05_impl(X, W, Y, y_dtype, partial, M, N, K, ldx, ldw, ldy, accumulate, swiglu, splits, status, none, stream);
+    return gemm_tcgen05_impl(X, W, Y, y_dtype, partial, M, N, K, ldx, ldw, ldy, accumulate, IkGlu(swiglu, glu_alpha, glu_limit, glu_shift),
+                             splits, status, none, stream);
 }
 
 // A grouped product: W stacks n_groups matrices [N, K]; the M rows of X lie in token tiles of `bn` rows (a multiple of 16

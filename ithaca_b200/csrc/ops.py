@@ -76,8 +76,8 @@ _SIGNATURES = {
     "ik_copy": [_vp, _vp, _u64, _vp],
     "ik_rope_append": [_vp, _vp, _i, _vp, _vp, _i, _vp, _vp, _vp, _i, _vp, _i, _i, _i, _i, _i, _i, _i, _i, _i, _vp, _vp],
     "ik_gemm_simt": [_vp, _i, _vp, _i, _vp, _i, _i, _i, _i, _i, _i, _i, _i, _vp],
-    "ik_gemm_bf16_mma": [_vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _i, _i, _i, _i, _vp],
-    "ik_gemm_tcgen05": [_vp, _vp, _vp, _i, _vp, _i, _i, _i, _i, _i, _i, _i, _i, _i, _vp, _vp],
+    "ik_gemm_bf16_mma": [_vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _i, _i, _i, _i, _f, _f, _f, _vp],
+    "ik_gemm_tcgen05": [_vp, _vp, _vp, _i, _vp, _i, _i, _i, _i, _i, _i, _i, _i, _f, _f, _f, _i, _vp, _vp],
     "ik_gemm_tcgen05_tile": [_i],
     "ik_gemm_tcgen05_tile_width": [_i, _i],
     "ik_gemm_tcgen05_stream_k_bytes": [],
@@ -340,10 +340,11 @@ def gemm_simt(x: torch.Tensor, w: torch.Tensor, out: Optional[torch.Tensor] = No
 
 
 def gemm_bf16_mma(x: torch.Tensor, w: torch.Tensor, out: Optional[torch.Tensor] = None, out_dtype=torch.float32,
-                  accumulate: bool = False, kind: int = 0, swiglu: bool = False) -> Optional[torch.Tensor]:
+                  accumulate: bool = False, kind: int = 0, swiglu: bool = False, glu=None) -> Optional[torch.Tensor]:
     """bfloat16 operands, float accumulation on the warp-level tensor-core path.  ``kind``: 0 = by
     M, 1 = the skinny (decode) kernel, 2 = the tiled kernel.  Returns None when the kernels
-    do not take these sizes (K not a multiple of 8, unaligned rows).
+    do not take these sizes (K not a multiple of 8, unaligned rows).  ``glu`` = (alpha, limit, shift) with ``swiglu``: the
+    epilogue joins gate and up as gate * sigmoid(alpha gate) * (up + shift), both limited, instead of silu(gate) * up.
 
     ``w`` is a weight: the skinny kernel, launched early, reads its first rows before it waits for the
     kernel before it in the stream, so ``w`` must not be what that kernel writes (``x`` and ``out`` may be)."""
@@ -362,8 +363,10 @@ def gemm_bf16_mma(x: torch.Tensor, w: torch.Tensor, out: Optional[torch.Tensor] 
     if out.shape != (M, n_out) or out.stride(1) != 1:
         raise KernelError("gemm: the output has the wrong shape")
     _work(f"gemm_skinny{' +swiglu' if swiglu else ''} {M}x{N}x{K}", 2 * (M * K + N * K) + M * n_out * out.element_size(), 2 * M * N * K)
+    ga, gl, gs = glu if glu is not None else (1.0, 0.0, 0.0)
     st = lib().ik_gemm_bf16_mma(_ptr(x), _ptr(w), _ptr(out), _code(out), M, N, K, x.stride(0), w.stride(0),
-                                out.stride(0), 1 if accumulate else 0, kind, 1 if swiglu else 0, _stream())
+                                out.stride(0), 1 if accumulate else 0, kind, (2 if glu is not None else 1) if swiglu else 0, ga, gl, gs,
+                                _stream())
     if st == -2:
         return None
     _check(st, "gemm_bf16_mma")
@@ -445,7 +448,7 @@ def pairs_lib():
             _pairs_lib = False
         else:
             l = build.pairs()
-            l.ik_gemm_tcgen05_pairs.argtypes = [_vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _i, _i, _i, _vp, _vp]
+            l.ik_gemm_tcgen05_pairs.argtypes = [_vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _i, _i, _i, _f, _f, _f, _vp, _vp]
             l.ik_gemm_tcgen05_pairs.restype = _i
             l.ik_gemm_qkv_rope_tcgen05_pairs.argtypes = [_vp, _vp, _i, _i, _i, _i, _i, _vp, _vp, _vp]
             l.ik_gemm_qkv_rope_tcgen05_pairs.restype = _i
@@ -455,7 +458,8 @@ def pairs_lib():
 
 def gemm_tcgen05(x: torch.Tensor, w: torch.Tensor, out: Optional[torch.Tensor] = None, out_dtype=torch.float32,
                  accumulate: bool = False, splits: Optional[int] = None,
-                 status: Optional[torch.Tensor] = None, swiglu: bool = False, pairs: Optional[bool] = None) -> Optional[torch.Tensor]:
+                 status: Optional[torch.Tensor] = None, swiglu: bool = False, pairs: Optional[bool] = None,
+                 glu=None) -> Optional[torch.Tensor]:
     """bfloat16 operands on the tcgen05 tensor cores (TMA-fed, accumulators in TMEM).  Returns None
     when the kernel does not take these sizes (K not a multiple of 8, unaligned rows).
 
@@ -479,6 +483,8 @@ def gemm_tcgen05(x: torch.Tensor, w: torch.Tensor, out: Optional[torch.Tensor] =
         raise KernelError("gemm: the output has the wrong shape")
     if splits is None:
         splits = tcgen05_splits(M, N, K)
+    join = (2 if glu is not None else 1) if swiglu else 0          # ``glu`` = (alpha, limit, shift): the gate with parameters
+    ga, gl, gs = glu if glu is not None else (1.0, 0.0, 0.0)
     if splits == 1 and M > 256 and pairs is not False:
         pl = pairs_lib()
         if pl is None and pairs:
@@ -486,7 +492,7 @@ def gemm_tcgen05(x: torch.Tensor, w: torch.Tensor, out: Optional[torch.Tensor] =
         if pl is not None:
             _work(f"gemm_tcgen05 pairs{' +swiglu' if swiglu else ''} {M}x{N}x{K}", 2 * (M * K + N * K) + M * n_out * out.element_size(), 2 * M * N * K)
             st = pl.ik_gemm_tcgen05_pairs(_ptr(x), _ptr(w), _ptr(out), _code(out), M, N, K, x.stride(0), w.stride(0),
-                                          out.stride(0), 1 if accumulate else 0, 1 if swiglu else 0, _ptr(status), _stream())
+                                          out.stride(0), 1 if accumulate else 0, join, ga, gl, gs, _ptr(status), _stream())
             if st != -2:
                 _check(st, "gemm_tcgen05 (pairs)")
                 return out
@@ -494,7 +500,7 @@ def gemm_tcgen05(x: torch.Tensor, w: torch.Tensor, out: Optional[torch.Tensor] =
                torch.empty((splits, M, N), dtype=torch.float32, device=x.device) if splits > 1 else None)
     _work(f"gemm_tcgen05{' +swiglu' if swiglu else ''} {M}x{N}x{K}", 2 * (M * K + N * K) + M * n_out * out.element_size(), 2 * M * N * K)
     st = lib().ik_gemm_tcgen05(_ptr(x), _ptr(w), _ptr(out), _code(out), _ptr(partial), M, N, K, x.stride(0),
-                               w.stride(0), out.stride(0), 1 if accumulate else 0, 1 if swiglu else 0, splits, _ptr(status),
+                               w.stride(0), out.stride(0), 1 if accumulate else 0, join, ga, gl, gs, splits, _ptr(status),
                                _stream())
     if st == -2:
         return None

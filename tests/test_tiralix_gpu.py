@@ -252,6 +252,33 @@ def test_gate_with_limits_and_logit_cap_kernels():
     assert rel_err(ops.scale_softcap_(v.clone(), 0.5, 0.0).cpu().numpy(), (v.cpu().double() * 0.5).numpy()) < 1e-7
 
 
+@pytest.mark.parametrize("T", [5, 12, 40, 300, 700])
+def test_gate_with_limits_in_the_products_epilogues(monkeypatch, T):
+    """The 16-bit feed-forward joins gate and up inside the product that makes them: the warp-level kernel for a few tokens,
+    the tcgen05 kernel above, its pair mode for many.  Inputs large enough that the limits bite."""
+    from ithaca_b200.config.spec import PartSpec
+    from ithaca_b200.csrc import ops
+    from ithaca_b200.parts import FEED_FORWARDS, Runtime
+    d, ff = 128, 328
+    g = torch.Generator().manual_seed(T)
+    spec = PartSpec("gated_mlp", {"hidden_size": d, "intermediate_size": ff, "activation": "swish", "alpha": 1.702, "limit": 1.0,
+                                  "up_shift": 1.0}, {"gate": "gate", "up": "up", "down": "down"})
+    t = {"gate": (torch.randn(ff, d, generator=g) * 0.15).bfloat16(), "up": (torch.randn(ff, d, generator=g) * 0.15).bfloat16(),
+         "down": (torch.randn(d, ff, generator=g) * 0.1).bfloat16()}
+    part = FEED_FORWARDS.get("gated_mlp")(spec, t, Runtime(dtype="bfloat16", device=DEV))
+
+    def never(*a, **k):
+        raise AssertionError("the gate ran as a kernel of its own")
+    monkeypatch.setattr(ops, "glu_act", never)
+    x = torch.randn(T, d, generator=g).bfloat16()
+    want = P.clamped_gated_ff(x.double(), {"limit": 1.0}, t, "")
+    out = torch.full((T, d), 7.0, device=DEV)
+    part.forward(x.to(DEV), None, out, accumulate=False)
+    assert rel_err(out.cpu().numpy(), want.numpy()) < 2e-2
+    free = P.clamped_gated_ff(x.double(), {"limit": 100.0}, t, "")
+    assert rel_err(free.numpy(), want.numpy()) > 0.1                      # the limits matter here
+
+
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
 @pytest.mark.parametrize("taps", [1, 2, 4])
 def test_causal_convolution_with_its_ring(dtype, taps):
