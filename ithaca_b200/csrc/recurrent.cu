@@ -158,14 +158,36 @@ template <bool FAST> __device__ __forceinline__ float ik_silu_as(float x) {
     return FAST ? x * __frcp_rn(1.0f + __expf(-x)) : x / (1.0f + expf(-x));
 }
 
-template <typename TU, typename TO, bool FAST, int NPT>
+// A load that is issued where it stands (the compiler may otherwise sink it to its first use, behind the tile's arithmetic).
+__device__ __forceinline__ float ik_ld_now(const float* p) { float v; asm volatile("ld.global.f32 %0, [%1];" : "=f"(v) : "l"(p)); return v; }
+// The 16-bit value stays as it was loaded until ik_raw_float turns it into a float where it is used: a conversion next to
+// the load would wait for the load.
+__device__ __forceinline__ unsigned short ik_ld_now(const __nv_bfloat16* p) {
+    unsigned short v;
+    asm volatile("ld.global.u16 %0, [%1];" : "=h"(v) : "l"(p));
+    return v;
+}
+__device__ __forceinline__ float ik_raw_float(float v) { return v; }
+__device__ __forceinline__ float ik_raw_float(unsigned short v) { return __uint_as_float((unsigned)v << 16); }
+template <typename T> struct IkRaw { typedef float type; };
+template <> struct IkRaw<__nv_bfloat16> { typedef unsigned short type; };
+template <bool FAST> __device__ __forceinline__ float ik_softplus_as(float x) {
+    return x > 20.0f ? x : (FAST ? __logf(1.0f + __expf(x)) : log1pf(expf(x)));
+}
+
+// NPT states a thread, L lanes a channel, TT tokens a tile: all fixed at compile time, so that the tile's layout and the
+// sum over lanes are constants.  Lane l holds states l*NPT .. l*NPT + NPT - 1; the L*NPT >= N places beyond N are padding
+// (A = 0, B = C = 0: they stay zero and add nothing), which spares every guard in the token loop.
+template <typename TU, typename TO, bool FAST, int NPT, int L, int TT>
 __global__ void __launch_bounds__(128)
 selective_scan_kernel(const TU* __restrict__ u, const float* __restrict__ dt_raw, const float* __restrict__ dt_bias,
                       const float* __restrict__ A, const float* __restrict__ bc, int ldbc, int b_off, int c_off,
                       const float* __restrict__ Dv, const float* __restrict__ z, int ldz, float* __restrict__ state,
                       const int* __restrict__ slots, const int* __restrict__ cu_seqlens, const int* __restrict__ kv_lens,
-                      TO* __restrict__ out, int inner, int N, int L, int TT, int np2_shift) {
-    extern __shared__ __align__(16) float sm[];      // [2][TT][3 CH + NP2]: x, dt, silu(z) per channel; B then C (padded to NP2)
+                      TO* __restrict__ out, int inner, int N) {
+    constexpr int CH = 128 / L, NPAD = L * NPT, W = 3 * CH + 2 * NPAD, PER_TILE = TT * W;
+    constexpr int KX = (TT * CH + 127) / 128, KB = (TT * 2 * NPAD + 127) / 128;      // staged values a thread
+    extern __shared__ __align__(16) float sm[];      // [2][TT][W]: x, dt, silu(z) per channel; B (padded), C (padded)
     ik_pdl_wait();
     IK_AFTER_WAIT(u);
     IK_AFTER_WAIT(dt_raw);
@@ -175,8 +197,7 @@ selective_scan_kernel(const TU* __restrict__ u, const float* __restrict__ dt_raw
     IK_AFTER_WAIT(cu_seqlens);
     IK_AFTER_WAIT(kv_lens);
     ik_pdl_launch_dependents();
-    const int b = blockIdx.y, CH = 128 / L, NP2 = 1 << np2_shift, W = 3 * CH + NP2;
-    const int chs = 31 - __clz(CH);
+    const int b = blockIdx.y;
     const int l = threadIdx.x & (L - 1), ch = threadIdx.x / L;
     const int c0 = blockIdx.x * CH, c = c0 + ch;
     const bool live = c < inner;
@@ -188,49 +209,54 @@ selective_scan_kernel(const TU* __restrict__ u, const float* __restrict__ dt_raw
     float S[NPT], a[NPT];
     #pragma unroll
     for (int r = 0; r < NPT; r++) {
-        const int n = l + L * r;
+        const int n = l * NPT + r;
         a[r] = n < N ? A[(size_t)cc * N + n] : 0.f;
         S[r] = (n < N && start > 0) ? st_in[n] : 0.f;
     }
     const float dskip = Dv ? Dv[cc] : 0.f;
-    const int per_tile = TT * W;
-    // staging: x, dt, z are TT x CH each (at most 512 elements: four per thread), B | C is TT x NP2 (at most 2048: sixteen)
-    float rx[4], rd[4], rz[4], rb[16];
+    typename IkRaw<TU>::type rx[KX];
+    float rd[KX], rz[KX], rb[KB], bias_k[KX];
+    #pragma unroll
+    for (int k = 0; k < KX; k++) {
+        const int col = c0 + ((threadIdx.x + k * 128) % CH);
+        bias_k[k] = (dt_bias && col < inner) ? dt_bias[col] : 0.f;
+    }
     auto fetch = [&](int t0) {
         #pragma unroll
-        for (int k = 0; k < 4; k++) {
-            const int e = threadIdx.x + k * 128, tt = e >> chs, col = c0 + (e & (CH - 1));
+        for (int k = 0; k < KX; k++) {
+            const int e = threadIdx.x + k * 128, tt = e / CH, col = c0 + e % CH;
             const int t = min(t0 + tt, hi - 1);
-            rx[k] = rd[k] = rz[k] = 0.f;
+            rx[k] = 0;
+            rd[k] = rz[k] = 0.f;
             if (tt < TT && col < inner) {
-                rx[k] = ik_ld(u, (size_t)t * inner + col);
-                rd[k] = dt_raw[(size_t)t * inner + col] + (dt_bias ? dt_bias[col] : 0.f);
-                if (z) rz[k] = z[(size_t)t * ldz + col];
+                rx[k] = ik_ld_now(u + (size_t)t * inner + col);
+                rd[k] = ik_ld_now(dt_raw + (size_t)t * inner + col);
+                if (z) rz[k] = ik_ld_now(z + (size_t)t * ldz + col);
             }
         }
         #pragma unroll
-        for (int k = 0; k < 16; k++) {
-            const int e = threadIdx.x + k * 128, tt = e >> np2_shift, n = e & (NP2 - 1);
+        for (int k = 0; k < KB; k++) {
+            const int e = threadIdx.x + k * 128, tt = e / (2 * NPAD), n2 = e % (2 * NPAD), n = n2 % NPAD;
             const int t = min(t0 + tt, hi - 1);
             rb[k] = 0.f;
-            if (tt < TT && n < 2 * N) rb[k] = n < N ? bc[(size_t)t * ldbc + b_off + n] : bc[(size_t)t * ldbc + c_off + n - N];
+            if (tt < TT && n < N) rb[k] = ik_ld_now(bc + (size_t)t * ldbc + (n2 < NPAD ? b_off : c_off) + n);
         }
     };
     auto store = [&](int buf) {
-        float* tile = sm + buf * per_tile;
+        float* tile = sm + buf * PER_TILE;
         #pragma unroll
-        for (int k = 0; k < 4; k++) {
-            const int e = threadIdx.x + k * 128, tt = e >> chs, w = e & (CH - 1);
+        for (int k = 0; k < KX; k++) {
+            const int e = threadIdx.x + k * 128, tt = e / CH, w = e % CH;
             if (tt < TT) {
-                tile[tt * W + w] = rx[k];
-                tile[tt * W + CH + w] = ik_softplus(rd[k]);
+                tile[tt * W + w] = ik_raw_float(rx[k]);
+                tile[tt * W + CH + w] = ik_softplus_as<FAST>(rd[k] + bias_k[k]);
                 tile[tt * W + 2 * CH + w] = ik_silu_as<FAST>(rz[k]);
             }
         }
         #pragma unroll
-        for (int k = 0; k < 16; k++) {
-            const int e = threadIdx.x + k * 128, tt = e >> np2_shift, n = e & (NP2 - 1);
-            if (tt < TT) tile[tt * W + 3 * CH + n] = rb[k];
+        for (int k = 0; k < KB; k++) {
+            const int e = threadIdx.x + k * 128, tt = e / (2 * NPAD), n2 = e % (2 * NPAD);
+            if (tt < TT) tile[tt * W + 3 * CH + n2] = rb[k];
         }
     };
     fetch(lo);
@@ -240,26 +266,48 @@ selective_scan_kernel(const TU* __restrict__ u, const float* __restrict__ dt_raw
     for (int t0 = lo; t0 < hi; t0 += TT, buf ^= 1) {
         if (t0 + TT < hi) fetch(t0 + TT);
         const int n_here = min(TT, hi - t0);
-        for (int tt = 0; tt < n_here; tt++) {
-            const float* row = sm + buf * per_tile + tt * W;
-            const float x = row[ch], dt = row[CH + ch], gz = row[2 * CH + ch];
-            const float dx = dt * x;
-            float acc0 = 0.f, acc1 = 0.f;
-            #pragma unroll
-            for (int r = 0; r < NPT; r++) {
-                const int n = l + L * r;
-                if (n < N) {
+        const float* tile = sm + buf * PER_TILE;
+        // the tile's tokens in order; a token's sum over this lane's states stays in a register, the lanes' sums are added
+        // for the whole tile afterwards (the shuffles are off the token-by-token chain)
+        float acc[TT];
+        #pragma unroll
+        for (int tt = 0; tt < TT; tt++) {
+            const float* row = tile + tt * W;
+            const float dt = row[CH + ch], dx = dt * row[ch];
+            float bv[NPT], cv[NPT];
+            if (NPT % 4 == 0) {
+                #pragma unroll
+                for (int r = 0; r < NPT; r += 4) {
+                    const float4 b4 = *reinterpret_cast<const float4*>(row + 3 * CH + l * NPT + r);
+                    const float4 c4 = *reinterpret_cast<const float4*>(row + 3 * CH + NPAD + l * NPT + r);
+                    bv[r] = b4.x; bv[r + 1] = b4.y; bv[r + 2] = b4.z; bv[r + 3] = b4.w;
+                    cv[r] = c4.x; cv[r + 1] = c4.y; cv[r + 2] = c4.z; cv[r + 3] = c4.w;
+                }
+            } else {
+                #pragma unroll
+                for (int r = 0; r < NPT; r++) { bv[r] = row[3 * CH + l * NPT + r]; cv[r] = row[3 * CH + NPAD + l * NPT + r]; }
+            }
+            float a0 = 0.f, a1 = 0.f;
+            if (tt < n_here) {
+                #pragma unroll
+                for (int r = 0; r < NPT; r++) {
                     const float da = FAST ? __expf(dt * a[r]) : expf(dt * a[r]);
-                    S[r] = fmaf(da, S[r], dx * row[3 * CH + n]);
-                    if (r & 1) acc1 = fmaf(S[r], row[3 * CH + N + n], acc1);
-                    else acc0 = fmaf(S[r], row[3 * CH + N + n], acc0);
+                    S[r] = fmaf(da, S[r], dx * bv[r]);
+                    if (r & 1) a1 = fmaf(S[r], cv[r], a1);
+                    else a0 = fmaf(S[r], cv[r], a0);
                 }
             }
-            float acc = acc0 + acc1;
-            for (int o = L >> 1; o > 0; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
-            if (l == 0 && live) {
-                float y = fmaf(dskip, x, acc);
-                if (z) y *= gz;
+            acc[tt] = a0 + a1;
+        }
+        #pragma unroll
+        for (int tt = 0; tt < TT; tt++) {
+            float v = acc[tt];
+            #pragma unroll
+            for (int o = L >> 1; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+            if (l == 0 && live && tt < n_here) {
+                const float* row = tile + tt * W;
+                float y = fmaf(dskip, row[ch], v);
+                if (z) y *= row[2 * CH + ch];
                 ik_st(out, (size_t)(t0 + tt) * inner + c, y);
             }
         }
@@ -269,10 +317,34 @@ selective_scan_kernel(const TU* __restrict__ u, const float* __restrict__ dt_raw
     if (live) {
         #pragma unroll
         for (int r = 0; r < NPT; r++) {
-            const int n = l + L * r;
+            const int n = l * NPT + r;
             if (n < N) st_out[n] = S[r];
         }
     }
+}
+
+template <typename TU, typename TO, bool FAST>
+static int launch_scan(const void* u, const float* dt_raw, const float* dt_bias, const float* A, const float* bc, int ldbc, int b_off,
+                       int c_off, const float* Dv, const float* z, int ldz, float* state, const int* slots, const int* cu_seqlens,
+                       const int* kv_lens, void* out, int B, int inner, int N, cudaStream_t stream) {
+    // four states a thread (eight from 65 states on), as many lanes a channel as that takes, tiles as long as a thread's
+    // staging registers allow
+#define IK_SCAN(NPT, L, TT)                                                                                                     \
+    do {                                                                                                                        \
+        constexpr int CH = 128 / (L), W = 3 * CH + 2 * (L) * (NPT);                                                             \
+        const dim3 grid((inner + CH - 1) / CH, B);                                                                              \
+        IK_RETURN_IF_ERROR(ik_launch(selective_scan_kernel<TU, TO, FAST, NPT, L, TT>, grid, 128, (size_t)2 * (TT) * W * sizeof(float), stream, \
+                                     (const TU*)u, dt_raw, dt_bias, A, bc, ldbc, b_off, c_off, Dv, z, ldz, state, slots, cu_seqlens,  \
+                                     kv_lens, (TO*)out, inner, N));                                                             \
+    } while (0)
+    if (N <= 16) IK_SCAN(4, 4, 16);
+    else if (N <= 32) IK_SCAN(4, 8, 16);
+    else if (N <= 64) IK_SCAN(4, 16, 16);
+    else if (N <= 128) IK_SCAN(8, 16, 8);
+    else if (N <= 256) IK_SCAN(8, 32, 4);
+    else return IK_UNSUPPORTED;
+#undef IK_SCAN
+    IK_LAUNCH_STATUS();
 }
 
 IK_EXPORT int ik_selective_scan(const void* u, int u_dtype, const float* dt_raw, const float* dt_bias, const float* A,
@@ -281,37 +353,13 @@ IK_EXPORT int ik_selective_scan(const void* u, int u_dtype, const float* dt_raw,
                                 int out_dtype, int T, int B, int inner, int N, cudaStream_t stream) {
     if (T < 0 || B < 0 || inner <= 0 || N <= 0 || !state || b_off < 0 || c_off < 0 || ldbc < N) return IK_BAD_ARGUMENT;
     if (T == 0 || B == 0) return IK_OK;
-    // two states a thread while a warp's lanes suffice for a channel (many short chains fill the SMs), else eight
-    const int npt = N <= 64 ? 2 : 8;
-    int L = 1;
-    while (L * npt < N) L *= 2;
-    if (L > 32) return IK_UNSUPPORTED;
-    const int CH = 128 / L;
-    int shift = 0;
-    while ((1 << shift) < 2 * N) shift++;
-    int TT = 16;
-    if (TT > 512 / CH) TT = 512 / CH;
-    if (TT > (2048 >> shift)) TT = 2048 >> shift;
-    if (TT < 1) return IK_UNSUPPORTED;
-    const int W = 3 * CH + (1 << shift);
-    const dim3 grid((inner + CH - 1) / CH, B);
-    const size_t smem = (size_t)2 * TT * W * sizeof(float);
-#define IK_SCAN(TU, TO, FAST)                                                                                               \
-    do {                                                                                                                    \
-        if (npt == 2)                                                                                                       \
-            IK_RETURN_IF_ERROR(ik_launch(selective_scan_kernel<TU, TO, FAST, 2>, grid, 128, smem, stream, (const TU*)u, dt_raw, dt_bias, A, bc, \
-                                         ldbc, b_off, c_off, Dv, z, ldz, state, slots, cu_seqlens, kv_lens, (TO*)out, inner, N, L, TT, shift)); \
-        else                                                                                                                \
-            IK_RETURN_IF_ERROR(ik_launch(selective_scan_kernel<TU, TO, FAST, 8>, grid, 128, smem, stream, (const TU*)u, dt_raw, dt_bias, A, bc, \
-                                         ldbc, b_off, c_off, Dv, z, ldz, state, slots, cu_seqlens, kv_lens, (TO*)out, inner, N, L, TT, shift)); \
-    } while (0)
-    if (u_dtype == IK_F32 && out_dtype == IK_F32) IK_SCAN(float, float, false);
-    else if (u_dtype == IK_BF16 && out_dtype == IK_BF16) IK_SCAN(__nv_bfloat16, __nv_bfloat16, true);
-    else if (u_dtype == IK_F32 && out_dtype == IK_BF16) IK_SCAN(float, __nv_bfloat16, false);
-    else if (u_dtype == IK_BF16 && out_dtype == IK_F32) IK_SCAN(__nv_bfloat16, float, true);
-    else return IK_BAD_ARGUMENT;
-#undef IK_SCAN
-    IK_LAUNCH_STATUS();
+#define IK_ARGS u, dt_raw, dt_bias, A, bc, ldbc, b_off, c_off, Dv, z, ldz, state, slots, cu_seqlens, kv_lens, out, B, inner, N, stream
+    if (u_dtype == IK_F32 && out_dtype == IK_F32) return launch_scan<float, float, false>(IK_ARGS);
+    if (u_dtype == IK_BF16 && out_dtype == IK_BF16) return launch_scan<__nv_bfloat16, __nv_bfloat16, true>(IK_ARGS);
+    if (u_dtype == IK_F32 && out_dtype == IK_BF16) return launch_scan<float, __nv_bfloat16, false>(IK_ARGS);
+    if (u_dtype == IK_BF16 && out_dtype == IK_F32) return launch_scan<__nv_bfloat16, float, true>(IK_ARGS);
+#undef IK_ARGS
+    return IK_BAD_ARGUMENT;
 }
 
 // ------------------------------------------------------------------ linear attention with a constant decay per head
@@ -325,9 +373,9 @@ IK_EXPORT int ik_selective_scan(const void* u, int u_dtype, const float* dt_raw,
 // where tiles begin.  FULL: dk = parts * RMAX and RMAX is a multiple of 4: no row is guarded and q, k come from shared
 // memory four at a time.
 constexpr int LA_ROWS = 2;         // token rows a warp stages per tile, at most
-constexpr int LA_PER_ROW = 17;     // 32-wide pieces of a staged row, at most: 2 dk + 32 <= 544
 
-template <int RMAX, bool FULL>
+// LA_PER_ROW: 32-wide pieces of a staged row (2 dk + 32 values): 9 up to dk = 128, 17 up to 256
+template <int RMAX, bool FULL, int LA_PER_ROW>
 __global__ void __launch_bounds__(512)
 decay_attention_kernel(const float* __restrict__ p, int ldp, int q_off, int k_off, int v_off, const float* __restrict__ decay,
                        float* __restrict__ state, const int* __restrict__ slots, const int* __restrict__ cu_seqlens,
@@ -382,10 +430,15 @@ decay_attention_kernel(const float* __restrict__ p, int ldp, int q_off, int k_of
             #pragma unroll
             for (int kk = 0; kk < LA_PER_ROW; kk++) {
                 const int w = j + 32 * kk;
-                if (tt >= TT || w >= W) continue;
-                const float x = regs[rr][kk];
-                sm[buf * per_tile + tt * W + w] = act == 2 ? ik_silu_as<true>(x) : act ? ik_silu_as<false>(x) : x;
+                if (tt < TT && w < W) sm[buf * per_tile + tt * W + w] = regs[rr][kk];
             }
+        }
+        if (!act) return;
+        // the activation on what this thread has just stored, in a loop that is not unrolled (one copy of its code)
+        for (int tt = part; tt < TT; tt += parts) {
+            float* row = sm + buf * per_tile + tt * W;
+            #pragma unroll 1
+            for (int w = j; w < W; w += 32) row[w] = act == 2 ? ik_silu_as<true>(row[w]) : ik_silu_as<false>(row[w]);
         }
     };
     fetch(lo);
@@ -459,20 +512,21 @@ IK_EXPORT int ik_decay_attention(const float* p, int ldp, int q_off, int k_off, 
     const dim3 grid(B, H, (dv + 31) / 32), block(32, parts);
     const size_t smem = (size_t)(2 * TT * W + 2 * TT * parts * 32) * sizeof(float);
     if (smem > 160 * 1024) return IK_UNSUPPORTED;
-#define IK_LA(RMAX, FULL)                                                                                                        \
+#define IK_LA(RMAX, FULL, PER_ROW)                                                                                               \
     do {                                                                                                                         \
         static bool raised = false;                                                                                              \
         if (smem > 48 * 1024 && !raised) {                                                                                       \
-            IK_RETURN_IF_ERROR(cudaFuncSetAttribute(decay_attention_kernel<RMAX, FULL>, cudaFuncAttributeMaxDynamicSharedMemorySize, 160 * 1024)); \
+            IK_RETURN_IF_ERROR(cudaFuncSetAttribute(decay_attention_kernel<RMAX, FULL, PER_ROW>, cudaFuncAttributeMaxDynamicSharedMemorySize, \
+                                                    160 * 1024));                                                                \
             raised = true;                                                                                                       \
         }                                                                                                                        \
-        IK_RETURN_IF_ERROR(ik_launch(decay_attention_kernel<RMAX, FULL>, grid, block, smem, stream, p, ldp, q_off, k_off, v_off, decay, state, \
-                                     slots, cu_seqlens, kv_lens, out, H, dk, dv, R, act, TT));                                    \
+        IK_RETURN_IF_ERROR(ik_launch(decay_attention_kernel<RMAX, FULL, PER_ROW>, grid, block, smem, stream, p, ldp, q_off, k_off, v_off, \
+                                     decay, state, slots, cu_seqlens, kv_lens, out, H, dk, dv, R, act, TT));                      \
     } while (0)
-    if (full && R == 8) IK_LA(8, true);
-    else if (full) IK_LA(16, true);
-    else if (R <= 8) IK_LA(8, false);
-    else IK_LA(16, false);
+    if (full && R == 8) IK_LA(8, true, 9);
+    else if (full) IK_LA(16, true, 17);
+    else if (R <= 8) IK_LA(8, false, 9);
+    else IK_LA(16, false, 17);
 #undef IK_LA
     IK_LAUNCH_STATUS();
 }
