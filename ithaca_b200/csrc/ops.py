@@ -109,8 +109,8 @@ _SIGNATURES = {
     "ik_scale_softcap": [_vp, _u64, _f, _f, _vp],
     "ik_glu_act": [_vp, _vp, _i, _i, _i, _i, _f, _f, _f, _vp],
     "ik_causal_conv": [_vp, _i, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _i, _vp],
-    "ik_selective_scan": [_vp, _i, _vp, _vp, _vp, _vp, _i, _i, _i, _vp, _vp, _i, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _vp],
-    "ik_decay_attention": [_vp, _i, _i, _i, _i, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _vp],
+    "ik_selective_scan": [_vp, _i, _vp, _vp, _vp, _vp, _i, _i, _i, _vp, _vp, _i, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _vp],
+    "ik_decay_attention": [_vp, _i, _i, _i, _i, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _i, _vp],
     "ik_norm_rope_append": [_vp, _i, _i, _i, _i, _vp, _vp, _f, _vp, _i, _vp, _vp, _i, _vp, _vp, _vp, _i, _vp, _f, _i, _i, _i, _i,
                             _i, _i, _i, _i, _i, _i, _vp, _vp],
     "ik_head_gate": [_vp, _vp, _i, _i, _vp, _i, _i, _i, _i, _i, _f, _vp],
@@ -1028,7 +1028,7 @@ def selective_scan(u: torch.Tensor, dt_raw: torch.Tensor, dt_bias: Optional[torc
           9 * T * inner * N)
     st = lib().ik_selective_scan(_ptr(u), _code(u), _ptr(dt_raw), _ptr(dt_bias), _ptr(A), _ptr(bc), bc.stride(0), b_off, c_off,
                                  _ptr(D), _ptr(z), ldz, _ptr(state), _ptr(ctx.slots), _ptr(ctx.cu_seqlens), _ptr(ctx.kv_lens),
-                                 _ptr(out), _code(out), T, ctx.n_seqs, inner, N, _stream())
+                                 _ptr(out), _code(out), T, ctx.n_seqs, inner, N, 1 if ctx.is_decode else 0, _stream())
     _check(st, "selective_scan")
     return out
 
@@ -1051,7 +1051,7 @@ def decay_attention(p: torch.Tensor, q_off: int, k_off: int, v_off: int, decay: 
           4 * T * n_heads * dk * dv)
     _check(lib().ik_decay_attention(_ptr(p), p.stride(0), q_off, k_off, v_off, _ptr(decay), _ptr(state), _ptr(ctx.slots),
                                     _ptr(ctx.cu_seqlens), _ptr(ctx.kv_lens), _ptr(out), T, ctx.n_seqs, n_heads, dk, dv,
-                                    int(act), _stream()), "decay_attention")
+                                    int(act), 1 if ctx.is_decode else 0, _stream()), "decay_attention")
     return out
 
 

@@ -323,16 +323,75 @@ selective_scan_kernel(const TU* __restrict__ u, const float* __restrict__ dt_raw
     }
 }
 
+// One token per sequence (a decode step): no tiles; every thread reads its own inputs and its NPT states, advances them and
+// writes them to the other parity's copy.  The arithmetic and its order are those of the kernel above, so a token gives
+// the same float32 bits whichever kernel runs it.
+template <typename TU, typename TO, bool FAST, int NPT, int L>
+__global__ void __launch_bounds__(128)
+selective_scan_decode_kernel(const TU* __restrict__ u, const float* __restrict__ dt_raw, const float* __restrict__ dt_bias,
+                             const float* __restrict__ A, const float* __restrict__ bc, int ldbc, int b_off, int c_off,
+                             const float* __restrict__ Dv, const float* __restrict__ z, int ldz, float* __restrict__ state,
+                             const int* __restrict__ slots, const int* __restrict__ cu_seqlens, const int* __restrict__ kv_lens,
+                             TO* __restrict__ out, int inner, int N) {
+    constexpr int CH = 128 / L;
+    ik_pdl_wait();
+    IK_AFTER_WAIT(u);
+    IK_AFTER_WAIT(dt_raw);
+    IK_AFTER_WAIT(bc);
+    IK_AFTER_WAIT(z);
+    IK_AFTER_WAIT(slots);
+    IK_AFTER_WAIT(cu_seqlens);
+    IK_AFTER_WAIT(kv_lens);
+    ik_pdl_launch_dependents();
+    const int b = blockIdx.y, l = threadIdx.x & (L - 1), c = blockIdx.x * CH + threadIdx.x / L;
+    const bool live = c < inner;
+    const int cc = live ? c : inner - 1;
+    const int t = cu_seqlens[b], end = kv_lens[b], start = end - 1;
+    const float* st_in = state + ((size_t)slots[b] * 2 + ((start - 1) & 1)) * inner * N + (size_t)cc * N;
+    float* st_out = state + ((size_t)slots[b] * 2 + ((end - 1) & 1)) * inner * N + (size_t)cc * N;
+    const float x = ik_ld(u, (size_t)t * inner + cc);
+    const float dt = ik_softplus_as<FAST>(dt_raw[(size_t)t * inner + cc] + (dt_bias ? dt_bias[cc] : 0.f));
+    const float dx = dt * x;
+    const float* row = bc + (size_t)t * ldbc;
+    float S[NPT], a0 = 0.f, a1 = 0.f;
+    #pragma unroll
+    for (int r = 0; r < NPT; r++) {
+        const int n = l * NPT + r;
+        if (n < N) {
+            const float ar = A[(size_t)cc * N + n];
+            S[r] = start > 0 ? st_in[n] : 0.f;
+            const float da = FAST ? __expf(dt * ar) : expf(dt * ar);
+            S[r] = fmaf(da, S[r], dx * row[b_off + n]);
+            if (r & 1) a1 = fmaf(S[r], row[c_off + n], a1);
+            else a0 = fmaf(S[r], row[c_off + n], a0);
+            if (live) st_out[n] = S[r];
+        }
+    }
+    float v = a0 + a1;
+    #pragma unroll
+    for (int o = L >> 1; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+    if (l == 0 && live) {
+        float y = fmaf(Dv ? Dv[cc] : 0.f, x, v);
+        if (z) y *= ik_silu_as<FAST>(z[(size_t)t * ldz + cc]);
+        ik_st(out, (size_t)t * inner + c, y);
+    }
+}
+
 template <typename TU, typename TO, bool FAST>
 static int launch_scan(const void* u, const float* dt_raw, const float* dt_bias, const float* A, const float* bc, int ldbc, int b_off,
                        int c_off, const float* Dv, const float* z, int ldz, float* state, const int* slots, const int* cu_seqlens,
-                       const int* kv_lens, void* out, int B, int inner, int N, cudaStream_t stream) {
+                       const int* kv_lens, void* out, int B, int inner, int N, int one_token_each, cudaStream_t stream) {
     // four states a thread (eight from 65 states on), as many lanes a channel as that takes, tiles as long as a thread's
     // staging registers allow
 #define IK_SCAN(NPT, L, TT)                                                                                                     \
     do {                                                                                                                        \
         constexpr int CH = 128 / (L), W = 3 * CH + 2 * (L) * (NPT);                                                             \
         const dim3 grid((inner + CH - 1) / CH, B);                                                                              \
+        if (one_token_each)                                                                                                     \
+            IK_RETURN_IF_ERROR(ik_launch(selective_scan_decode_kernel<TU, TO, FAST, NPT, L>, grid, 128, 0, stream, (const TU*)u, dt_raw,   \
+                                         dt_bias, A, bc, ldbc, b_off, c_off, Dv, z, ldz, state, slots, cu_seqlens, kv_lens, (TO*)out,    \
+                                         inner, N));                                                                            \
+        else                                                                                                                    \
         IK_RETURN_IF_ERROR(ik_launch(selective_scan_kernel<TU, TO, FAST, NPT, L, TT>, grid, 128, (size_t)2 * (TT) * W * sizeof(float), stream, \
                                      (const TU*)u, dt_raw, dt_bias, A, bc, ldbc, b_off, c_off, Dv, z, ldz, state, slots, cu_seqlens,  \
                                      kv_lens, (TO*)out, inner, N));                                                             \
@@ -350,10 +409,11 @@ static int launch_scan(const void* u, const float* dt_raw, const float* dt_bias,
 IK_EXPORT int ik_selective_scan(const void* u, int u_dtype, const float* dt_raw, const float* dt_bias, const float* A,
                                 const float* bc, int ldbc, int b_off, int c_off, const float* Dv, const float* z, int ldz,
                                 float* state, const int* slots, const int* cu_seqlens, const int* kv_lens, void* out,
-                                int out_dtype, int T, int B, int inner, int N, cudaStream_t stream) {
+                                int out_dtype, int T, int B, int inner, int N, int one_token_each, cudaStream_t stream) {
     if (T < 0 || B < 0 || inner <= 0 || N <= 0 || !state || b_off < 0 || c_off < 0 || ldbc < N) return IK_BAD_ARGUMENT;
     if (T == 0 || B == 0) return IK_OK;
-#define IK_ARGS u, dt_raw, dt_bias, A, bc, ldbc, b_off, c_off, Dv, z, ldz, state, slots, cu_seqlens, kv_lens, out, B, inner, N, stream
+    if (one_token_each && T != B) return IK_BAD_ARGUMENT;
+#define IK_ARGS u, dt_raw, dt_bias, A, bc, ldbc, b_off, c_off, Dv, z, ldz, state, slots, cu_seqlens, kv_lens, out, B, inner, N, one_token_each, stream
     if (u_dtype == IK_F32 && out_dtype == IK_F32) return launch_scan<float, float, false>(IK_ARGS);
     if (u_dtype == IK_BF16 && out_dtype == IK_BF16) return launch_scan<__nv_bfloat16, __nv_bfloat16, true>(IK_ARGS);
     if (u_dtype == IK_F32 && out_dtype == IK_BF16) return launch_scan<float, __nv_bfloat16, false>(IK_ARGS);
@@ -497,12 +557,79 @@ decay_attention_kernel(const float* __restrict__ p, int ldp, int q_off, int k_of
     }
 }
 
+// One token per sequence (a decode step): no tiles and few registers, so that several blocks share an SM and the state
+// streams.  q and k pass the activation once per block (shared memory), every thread advances its R rows of its column
+// and writes them to the other parity's copy.  The arithmetic and its order are those of the kernel above.
+template <int RMAX>
+__global__ void __launch_bounds__(512)
+decay_attention_decode_kernel(const float* __restrict__ p, int ldp, int q_off, int k_off, int v_off, const float* __restrict__ decay,
+                              float* __restrict__ state, const int* __restrict__ slots, const int* __restrict__ cu_seqlens,
+                              const int* __restrict__ kv_lens, float* __restrict__ out, int H, int dk, int dv, int R, int act) {
+    extern __shared__ __align__(16) float sm[];          // [2 dk] q, k;  [parts][32] partial sums
+    ik_pdl_wait();
+    IK_AFTER_WAIT(p);
+    IK_AFTER_WAIT(slots);
+    IK_AFTER_WAIT(cu_seqlens);
+    IK_AFTER_WAIT(kv_lens);
+    ik_pdl_launch_dependents();
+    const int b = blockIdx.x, h = blockIdx.y, j = threadIdx.x, part = threadIdx.y, parts = blockDim.y;
+    const int col0 = blockIdx.z * 32, col = col0 + j;
+    const bool live = col < dv;
+    const int ccol = live ? col : dv - 1;
+    const int tid = part * 32 + j, nthreads = parts * 32;
+    float* partial = sm + 2 * dk;
+    const int t = cu_seqlens[b], end = kv_lens[b], start = end - 1;
+    const size_t per = (size_t)H * dk * dv;
+    const float* st_in = state + ((size_t)slots[b] * 2 + ((start - 1) & 1)) * per + (size_t)h * dk * dv;
+    float* st_out = state + ((size_t)slots[b] * 2 + ((end - 1) & 1)) * per + (size_t)h * dk * dv;
+    float S[RMAX];
+    #pragma unroll
+    for (int r = 0; r < RMAX; r++) {
+        const int i = part * R + r;
+        S[r] = (r < R && i < dk && start > 0) ? st_in[(size_t)i * dv + ccol] : 0.f;
+    }
+    const float* row = p + (size_t)t * ldp;
+    for (int e = tid; e < 2 * dk; e += nthreads) {
+        const float x = e < dk ? row[q_off + h * dk + e] : row[k_off + h * dk + e - dk];
+        sm[e] = act == 2 ? ik_silu_as<true>(x) : act ? ik_silu_as<false>(x) : x;
+    }
+    float v = row[v_off + h * dv + ccol];
+    v = act == 2 ? ik_silu_as<true>(v) : act ? ik_silu_as<false>(v) : v;
+    const float a = decay[h];
+    __syncthreads();
+    const float* q = sm + part * R;
+    const float* k = q + dk;
+    float acc0 = 0.f, acc1 = 0.f;
+    #pragma unroll
+    for (int r = 0; r < RMAX; r++) {
+        if (r < R && part * R + r < dk) {
+            S[r] = fmaf(a, S[r], k[r] * v);
+            if (r & 1) acc1 = fmaf(S[r], q[r], acc1);
+            else acc0 = fmaf(S[r], q[r], acc0);
+            if (live) st_out[(size_t)(part * R + r) * dv + col] = S[r];
+        }
+    }
+    const float acc = acc0 + acc1;
+    if (parts == 1) {
+        if (live) out[(size_t)t * H * dv + h * dv + col] = acc;
+        return;
+    }
+    partial[part * 32 + j] = acc;
+    __syncthreads();
+    if (part == 0 && live) {
+        float o = 0.f;
+        for (int pp = 0; pp < parts; pp++) o += partial[pp * 32 + j];
+        out[(size_t)t * H * dv + h * dv + col] = o;
+    }
+}
+
 IK_EXPORT int ik_decay_attention(const float* p, int ldp, int q_off, int k_off, int v_off, const float* decay, float* state,
                                  const int* slots, const int* cu_seqlens, const int* kv_lens, float* out, int T, int B, int H,
-                                 int dk, int dv, int act, cudaStream_t stream) {
+                                 int dk, int dv, int act, int one_token_each, cudaStream_t stream) {
     if (T < 0 || B < 0 || H <= 0 || dk <= 0 || dv <= 0 || !state || !decay) return IK_BAD_ARGUMENT;
     if (T == 0 || B == 0) return IK_OK;
     if (dk > 256) return IK_UNSUPPORTED;
+    if (one_token_each && T != B) return IK_BAD_ARGUMENT;
     int parts = (dk + 7) / 8;                       // eight rows a thread ...
     if (parts > 16) parts = 16;                     // ... sixteen from 129 rows on
     const int R = (dk + parts - 1) / parts, W = 2 * dk + 32;
@@ -510,6 +637,16 @@ IK_EXPORT int ik_decay_attention(const float* p, int ldp, int q_off, int k_off, 
     if (TT > 16) TT = 16;
     const bool full = dk == parts * R && (R == 8 || R == 16) && ldp % 4 == 0;
     const dim3 grid(B, H, (dv + 31) / 32), block(32, parts);
+    if (one_token_each) {
+        const size_t smem1 = (size_t)(2 * dk + parts * 32) * sizeof(float);
+        if (R <= 8)
+            IK_RETURN_IF_ERROR(ik_launch(decay_attention_decode_kernel<8>, grid, block, smem1, stream, p, ldp, q_off, k_off, v_off, decay, state,
+                                         slots, cu_seqlens, kv_lens, out, H, dk, dv, R, act));
+        else
+            IK_RETURN_IF_ERROR(ik_launch(decay_attention_decode_kernel<16>, grid, block, smem1, stream, p, ldp, q_off, k_off, v_off, decay, state,
+                                         slots, cu_seqlens, kv_lens, out, H, dk, dv, R, act));
+        IK_LAUNCH_STATUS();
+    }
     const size_t smem = (size_t)(2 * TT * W + 2 * TT * parts * 32) * sizeof(float);
     if (smem > 160 * 1024) return IK_UNSUPPORTED;
 #define IK_LA(RMAX, FULL, PER_ROW)                                                                                               \
