@@ -47,6 +47,8 @@ class DecayAttention:
         self.n_heads = int(spec["n_heads"])
         self.head_dim = int(spec["head_dim"])
         self.v_head_dim = int(spec["v_head_dim"])
+        if self.head_dim > 256:
+            raise ValueError(f"decay_attention: the kernels hold a head's key rows in registers, up to 256 of them; found {self.head_dim}")
         decay = [float(a) for a in spec["decay"]]
         if len(decay) != self.n_heads:
             raise ValueError(f"decay_attention: {len(decay)} decays for {self.n_heads} heads")

@@ -49,6 +49,8 @@ class SelectiveScan:
         self.n_state = int(spec["state"])
         self.dt_rank = int(spec["dt_rank"])
         self.taps = int(spec["conv_taps"])
+        if self.n_state > 256:
+            raise ValueError(f"mamba1: the kernels hold a channel's states in one warp's registers, up to 256 of them; found {self.n_state}")
         w = spec.weights
         self.in_proj = Linear([tensors[w["in"]]], runtime)
         self.x_proj = Linear([tensors[w["x"]]], runtime)
