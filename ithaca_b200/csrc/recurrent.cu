@@ -178,6 +178,14 @@ template <bool FAST> __device__ __forceinline__ float ik_softplus_as(float x) {
 // NPT states a thread, L lanes a channel, TT tokens a tile: all fixed at compile time, so that the tile's layout and the
 // sum over lanes are constants.  Lane l holds states l*NPT .. l*NPT + NPT - 1; the L*NPT >= N places beyond N are padding
 // (A = 0, B = C = 0: they stay zero and add nothing), which spares every guard in the token loop.
+// One state's step, S <- exp(dt a) S + dt x B.  16-bit path: float, with the hardware's exponential.  float32 path: the
+// factor and the update are formed in double and rounded to float once, so that a step's error is half a unit in the last
+// place and has no bias that could add up over thousands of steps (the state itself stays a float).
+template <bool FAST> __device__ __forceinline__ float ik_scan_step(float S, float dt, float x, float a, float B) {
+    if (FAST) return fmaf(__expf(dt * a), S, dt * x * B);
+    return (float)fma(exp((double)dt * (double)a), (double)S, (double)dt * (double)x * (double)B);
+}
+
 template <typename TU, typename TO, bool FAST, int NPT, int L, int TT>
 __global__ void __launch_bounds__(128)
 selective_scan_kernel(const TU* __restrict__ u, const float* __restrict__ dt_raw, const float* __restrict__ dt_bias,
@@ -273,7 +281,7 @@ selective_scan_kernel(const TU* __restrict__ u, const float* __restrict__ dt_raw
         #pragma unroll
         for (int tt = 0; tt < TT; tt++) {
             const float* row = tile + tt * W;
-            const float dt = row[CH + ch], dx = dt * row[ch];
+            const float dt = row[CH + ch], x = row[ch];
             float bv[NPT], cv[NPT];
             if (NPT % 4 == 0) {
                 #pragma unroll
@@ -291,8 +299,7 @@ selective_scan_kernel(const TU* __restrict__ u, const float* __restrict__ dt_raw
             if (tt < n_here) {
                 #pragma unroll
                 for (int r = 0; r < NPT; r++) {
-                    const float da = FAST ? __expf(dt * a[r]) : expf(dt * a[r]);
-                    S[r] = fmaf(da, S[r], dx * bv[r]);
+                    S[r] = ik_scan_step<FAST>(S[r], dt, x, a[r], bv[r]);
                     if (r & 1) a1 = fmaf(S[r], cv[r], a1);
                     else a0 = fmaf(S[r], cv[r], a0);
                 }
@@ -351,7 +358,6 @@ selective_scan_decode_kernel(const TU* __restrict__ u, const float* __restrict__
     float* st_out = state + ((size_t)slots[b] * 2 + ((end - 1) & 1)) * inner * N + (size_t)cc * N;
     const float x = ik_ld(u, (size_t)t * inner + cc);
     const float dt = ik_softplus_as<FAST>(dt_raw[(size_t)t * inner + cc] + (dt_bias ? dt_bias[cc] : 0.f));
-    const float dx = dt * x;
     const float* row = bc + (size_t)t * ldbc;
     float S[NPT], a0 = 0.f, a1 = 0.f;
     #pragma unroll
@@ -360,8 +366,7 @@ selective_scan_decode_kernel(const TU* __restrict__ u, const float* __restrict__
         if (n < N) {
             const float ar = A[(size_t)cc * N + n];
             S[r] = start > 0 ? st_in[n] : 0.f;
-            const float da = FAST ? __expf(dt * ar) : expf(dt * ar);
-            S[r] = fmaf(da, S[r], dx * row[b_off + n]);
+            S[r] = ik_scan_step<FAST>(S[r], dt, x, ar, row[b_off + n]);
             if (r & 1) a1 = fmaf(S[r], row[c_off + n], a1);
             else a0 = fmaf(S[r], row[c_off + n], a0);
             if (live) st_out[n] = S[r];
